@@ -20,7 +20,7 @@ from dataclasses import dataclass
 
 import torch
 
-from ..parts.base import FixedState, PagedKV
+from ..parts.base import FixedState, PagedKV, cache_leaves
 from .manager import GroupSpec, PageCopy
 
 
@@ -28,12 +28,13 @@ from .manager import GroupSpec, PageCopy
 class LayerCache:
     """What a mixer gets for one run of its layer."""
 
-    kind: str                         # "paged_kv" | "fixed_state"
+    kind: str                         # "paged_kv" | "fixed_state" | "parts" (a mixer made of several: see `parts`)
     group: int                        # index of the block table to use (paged_kv)
     owner: bool                       # False: reads another run's cache, writes nothing
     kv: torch.Tensor | None = None    # [pages, 2, kv_heads, page_size, head_dim]
     state: torch.Tensor | None = None  # [slots, *shape]
     window: int | None = None
+    parts: tuple | None = None        # the views of a composite mixer's parts, in the order of its requirement
 
 
 class CacheStorage:
@@ -44,38 +45,53 @@ class CacheStorage:
                  num_state_slots: int = 0):
         self.page_size, self.dtype, self.device = page_size, dtype, torch.device(device)
         self.num_pages = num_pages
-        # group paged requirements: same (heads, head_dim, window, chunk) -> same group
+        # group paged requirements: same (heads, head_dim, window, chunk) -> same group.  A mixer made of several
+        # gives a tuple of requirements; every single need gets memory of its own and the run a view with `parts`.
         self.group_keys: list[PagedKV] = []
-        members: list[list[int]] = []
+        counts: list[int] = []
         for slot in cache_slots:
-            if slot.shares is None and isinstance(slot.requirement, PagedKV):
-                if slot.requirement not in self.group_keys:
-                    self.group_keys.append(slot.requirement)
-                    members.append([])
-                members[self.group_keys.index(slot.requirement)].append(slot.entry)
+            if slot.shares is None:
+                for req in cache_leaves(slot.requirement):
+                    if isinstance(req, PagedKV):
+                        if req not in self.group_keys:
+                            self.group_keys.append(req)
+                            counts.append(0)
+                        counts[self.group_keys.index(req)] += 1
         self.pools: list[torch.Tensor] = []
-        for key, entries in zip(self.group_keys, members):
-            shape = (len(entries), num_pages, 2, key.num_kv_heads, page_size, key.head_dim)
+        for key, n in zip(self.group_keys, counts):
+            shape = (n, num_pages, 2, key.num_kv_heads, page_size, key.head_dim)
             self.pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
         self.layer_caches: list[LayerCache | None] = [None] * len(cache_slots)
         self.num_state_slots = 0
-        for slot in cache_slots:
-            req = slot.requirement
-            if slot.shares is not None:
-                continue
+        self._states: list[torch.Tensor] = []
+        taken = [0] * len(self.group_keys)
+
+        def view(req):
+            if isinstance(req, tuple):
+                return LayerCache("parts", -1, True, parts=tuple(view(r) for r in req))
             if isinstance(req, PagedKV):
                 g = self.group_keys.index(req)
-                self.layer_caches[slot.entry] = LayerCache(
-                    "paged_kv", g, True, kv=self.pools[g][members[g].index(slot.entry)], window=req.window)
-            elif isinstance(req, FixedState):
+                taken[g] += 1
+                return LayerCache("paged_kv", g, True, kv=self.pools[g][taken[g] - 1], window=req.window)
+            if isinstance(req, FixedState):
                 self.num_state_slots = max(1, num_state_slots)
                 state = torch.zeros((self.num_state_slots, *req.shape), dtype=req.dtype, device=self.device)
-                self.layer_caches[slot.entry] = LayerCache("fixed_state", -1, True, state=state)
+                self._states.append(state)
+                return LayerCache("fixed_state", -1, True, state=state)
+            return None
+
+        def reader(src):
+            if src is None:
+                return None
+            return LayerCache(src.kind, src.group, False, kv=src.kv, state=src.state, window=src.window,
+                              parts=tuple(reader(p) for p in src.parts) if src.parts is not None else None)
+
+        for slot in cache_slots:
+            if slot.shares is None:
+                self.layer_caches[slot.entry] = view(slot.requirement)
         for slot in cache_slots:
             if slot.shares is not None:
-                src = self.layer_caches[slot.shares]
-                self.layer_caches[slot.entry] = LayerCache(src.kind, src.group, False, kv=src.kv, state=src.state,
-                                                           window=src.window)
+                self.layer_caches[slot.entry] = reader(self.layer_caches[slot.shares])
 
     @property
     def num_groups(self) -> int:
@@ -91,8 +107,8 @@ class CacheStorage:
     @staticmethod
     def page_bytes_for(cache_slots, page_size: int, dtype: torch.dtype) -> int:
         elem = torch.tensor([], dtype=dtype).element_size()
-        return sum(2 * s.requirement.num_kv_heads * s.requirement.head_dim * page_size * elem
-                   for s in cache_slots if s.shares is None and isinstance(s.requirement, PagedKV))
+        return sum(2 * r.num_kv_heads * r.head_dim * page_size * elem
+                   for s in cache_slots if s.shares is None for r in cache_leaves(s.requirement) if isinstance(r, PagedKV))
 
     def fill(self, value: float) -> None:
         """Overwrite every page (tests poison the pool to show stale reads)."""
@@ -108,7 +124,7 @@ class CacheStorage:
                 ops.copy_pages(self.pools[g], pairs)
 
     def _state_tensors(self):
-        return [lc.state for lc in self.layer_caches if lc is not None and lc.kind == "fixed_state" and lc.owner]
+        return self._states
 
     def zero_state(self, slots) -> None:
         """Zero the state of the given slots (an int or a list of them) in every stateful run:

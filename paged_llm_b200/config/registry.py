@@ -62,6 +62,10 @@ def _register_builtin() -> None:
     from .rokarax import RokaraxConfig
     if "Rokarax" not in ARCHITECTURES:
         register_architecture("Rokarax", RokaraxConfig, rokarax_spec)
+    from ..models.munazen import munazen_spec
+    from .munazen import MunazenConfig
+    if "Munazen" not in ARCHITECTURES:
+        register_architecture("Munazen", MunazenConfig, munazen_spec)
 
 
 _register_builtin()

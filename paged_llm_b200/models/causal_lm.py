@@ -13,7 +13,7 @@ from dataclasses import dataclass
 import torch
 
 from ..parts.base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, FixedState,
-                          LazyLinear, ModelSpec, PagedKV, PartSpec, TensorSpec, make_part, materialize)
+                          LazyLinear, ModelSpec, PagedKV, PartSpec, TensorSpec, cache_leaves, make_part, materialize)
 
 
 @dataclass(frozen=True)
@@ -21,16 +21,22 @@ class CacheSlot:
     """What one scheduled run of a layer needs from the cache manager."""
 
     entry: int                                   # index into the schedule
-    requirement: PagedKV | FixedState | None
+    requirement: PagedKV | FixedState | tuple | None   # a tuple: one requirement per part of a composite mixer
     shares: int | None                           # schedule entry whose cache is read instead
 
 
 def _resolve_positions(spec: PartSpec, positions: dict) -> dict:
+    """A part's `position` parameter (and any parameter whose name ends in `_position`) names a position encoding; the
+    part gets the object.  Parts given as parameters of a part (a mixer made of mixers) are looked through too."""
     extra = {}
     params = dict(spec.params)
-    if "position" in params:
-        name = params.pop("position")
-        extra["position"] = positions[name] if name is not None else None
+    for key, value in list(params.items()):
+        if key == "position" or key.endswith("_position"):
+            params.pop(key)
+            extra[key] = positions[value] if value is not None else None
+        elif isinstance(value, PartSpec):
+            inner, inner_extra = _resolve_positions(value, positions)
+            params[key] = PartSpec(inner.kind, dict(inner.params, **inner_extra), inner.weights)
     return PartSpec(spec.kind, params, spec.weights), extra
 
 
@@ -47,11 +53,15 @@ class CausalLM:
             mixer = make_part(MIXERS, "mixer", mixer_spec, **extra)
             ffn = make_part(FEED_FORWARDS, "feed-forward", layer.feed_forward) if layer.feed_forward is not None else None
             norms = {k: make_part(NORMS, "norm", ns) for k, ns in layer.norms.items()}
+            if isinstance(layer.block, PartSpec):        # an arrangement with parameters and tensors of its own
+                block_kind, block_args = layer.block.kind, dict(layer.block.params, weights=layer.block.weights)
+            else:
+                block_kind, block_args = layer.block, {}
             try:
-                block_cls = BLOCKS[layer.block]
+                block_cls = BLOCKS[block_kind]
             except KeyError:
-                raise KeyError(f"unknown block {layer.block!r}; registered: {sorted(BLOCKS)}") from None
-            self.blocks.append(block_cls(mixer, ffn, norms))
+                raise KeyError(f"unknown block {block_kind!r}; registered: {sorted(BLOCKS)}") from None
+            self.blocks.append(block_cls(mixer, ffn, norms, **block_args))
         self.final_norm = make_part(NORMS, "norm", spec.final_norm)
         self.head = make_part(HEADS, "head", spec.head)
         self.schedule = list(spec.schedule)
@@ -107,7 +117,7 @@ class CausalLM:
     @property
     def has_fixed_state(self) -> bool:
         """True if a scheduled run keeps per-request state of fixed size (the engine then holds state slots)."""
-        return any(isinstance(slot.requirement, FixedState) for slot in self.cache_slots())
+        return any(isinstance(r, FixedState) for slot in self.cache_slots() for r in cache_leaves(slot.requirement))
 
     # ---- forward ---------------------------------------------------------------
     def forward(self, ctx) -> torch.Tensor | None:

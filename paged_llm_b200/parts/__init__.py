@@ -3,13 +3,14 @@ built-in ones."""
 
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block, Embedding, FeedForward, FixedState,
                    Head, LayerSpec, LazyLinear, LazyNormed, materialize, Mixer, ModelSpec, Norm, PagedKV, Part, PartSpec, PositionEncoding, ScheduleEntry,
-                   TensorSpec, make_part, register_block, register_embedding, register_feed_forward, register_head, register_mixer, register_norm,
+                   StreamBranch, TensorSpec, cache_leaves, make_part, register_block, register_embedding, register_feed_forward, register_head, register_mixer, register_norm,
                    register_position_encoding)
-from . import attention, block, embedding, latent_attention, mlp, norm, rope, routed_mlp, ssm  # noqa: F401  (registration)
+from . import (attention, block, embedding, latent_attention, linear_attention, mlp, norm, parallel, recurrent, rope,  # noqa: F401
+               routed_mlp, ssm)  # noqa: F401  (registration)
 
 __all__ = [
     "BLOCKS", "EMBEDDINGS", "FEED_FORWARDS", "HEADS", "MIXERS", "NORMS", "POSITION_ENCODINGS", "Block", "Embedding", "FeedForward", "FixedState",
     "Head", "LayerSpec", "LazyLinear", "LazyNormed", "materialize", "Mixer", "ModelSpec", "Norm", "PagedKV", "Part", "PartSpec", "PositionEncoding", "ScheduleEntry",
-    "TensorSpec", "make_part", "register_block", "register_embedding", "register_feed_forward", "register_head", "register_mixer", "register_norm",
+    "StreamBranch", "TensorSpec", "cache_leaves", "make_part", "register_block", "register_embedding", "register_feed_forward", "register_head", "register_mixer", "register_norm",
     "register_position_encoding",
 ]

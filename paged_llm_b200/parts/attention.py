@@ -215,3 +215,84 @@ class GatedAttention(Mixer):
         g0 = nh * d + (0 if self.shares_cache else nkv * (d + dv))
         o = ops.head_gate(o, nh, D, dv, proj[:, g0:g0 + nh * dv] if self.gate else None)
         return LazyLinear(o, self.w_o)
+
+
+@register_mixer("rotated_value_attention")
+class RotatedValueAttention(Mixer):
+    """Grouped-query softmax attention over the paged cache whose values carry their position too:
+
+    * q, k, v and the output projection have biases (`bias`);
+    * q and k are rotated by `position` (any table of this package: partial rotation, either pairing, YaRN);
+    * the value of position j is rotated by j over all its `value_dim` elements with the angles of `value_position`
+      and cached so; a head's output at position i (the weighted sum of rotated values) is turned back by -i, so that
+      what the output sees of a value depends on the distance i - j only;
+    * with `head_gate`, head h's output is multiplied by sigmoid(w_g[h] . input), one number per head, after the
+      turn back and in front of the output projection;
+    * keys and values may differ in size; the cache and the attention kernel run at the larger of the two rounded
+      up to 16, the shorter vectors padded with zeros.
+    """
+
+    accepts_lazy_input = False
+
+    def __init__(self, weights: dict[str, str], hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 value_dim: int, scale: float, position=None, value_position=None, bias: bool = True,
+                 head_gate: bool = True, window: int | None = None):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.head_dim, self.value_dim, self.scale = head_dim, value_dim, float(scale)
+        self.position, self.value_position = position, value_position
+        if value_position is not None and (value_position.rotary_dim != value_dim or value_dim % 2):
+            raise ValueError(f"values of {value_dim} elements are rotated as a whole; the table turns "
+                             f"{value_position.rotary_dim}")
+        self.bias, self.head_gate = bool(bias), bool(head_gate)
+        self.window = int(window) if window else None
+        self.cache_dim = pad16(max(head_dim, value_dim))
+        if self.cache_dim > MAX_HEAD_DIM:
+            raise ValueError(f"head sizes {head_dim} / {value_dim}: the attention kernels take heads of at most {MAX_HEAD_DIM}")
+        self.names = weights
+        self.w_in = self.b_in = self.w_o = self.b_o = None
+
+    def cache_requirement(self):
+        return PagedKV(self.num_kv_heads, self.cache_dim, self.window)
+
+    def attention_plan_key(self):
+        return (self.num_heads // self.num_kv_heads, self.num_kv_heads, self.window, self.cache_dim)
+
+    def _stack(self):
+        return ["q_proj", "k_proj", "v_proj"] + (["g_proj"] if self.head_gate else [])
+
+    def tensor_specs(self):
+        h, d, dv, n = self.hidden_size, self.head_dim, self.value_dim, self.names
+        out = {n["q_proj"]: TensorSpec((self.num_heads * d, h)), n["k_proj"]: TensorSpec((self.num_kv_heads * d, h)),
+               n["v_proj"]: TensorSpec((self.num_kv_heads * dv, h)), n["o_proj"]: TensorSpec((h, self.num_heads * dv))}
+        if self.head_gate:
+            out[n["g_proj"]] = TensorSpec((self.num_heads, h))
+        if self.bias:
+            for k in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                out[n[k + "_bias"]] = TensorSpec((out[n[k]].shape[0],), role="vector", init="norm_zero")
+        return out
+
+    def load(self, tensors):
+        n = self.names
+        self.w_in = torch.cat([tensors[n[k]] for k in self._stack()], dim=0).contiguous()
+        self.w_o = tensors[n["o_proj"]].contiguous()
+        if self.bias:
+            self.b_in = torch.cat([tensors[n[k + "_bias"]].float() for k in ("q_proj", "k_proj", "v_proj")]).contiguous()
+            self.b_o = tensors[n["o_proj_bias"]].float().contiguous()
+
+    def bytes_read_per_step(self):
+        return sum(w.numel() * w.element_size() for w in (self.w_in, self.w_o))
+
+    def forward(self, h, ctx, cache):
+        ops = ctx.ops
+        nh, nkv, d, dv, D = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.cache_dim
+        block_table = ctx.block_tables[cache.group]
+        proj = ops.linear(h, self.w_in)                                     # [T, q | k | v | gate]
+        q = ops.rotated_qkv_write(proj, self.b_in, nh, nkv, d, dv, D, self.position, self.value_position, ctx, cache.kv,
+                                  block_table, write=cache.owner)
+        o = ops.paged_attention(q, nh, nkv, D, cache.kv, block_table, ctx, self.scale, self.window)
+        g0 = nh * d + nkv * (d + dv)
+        o = ops.head_unrotate_gate(o, nh, D, dv, self.value_position, ctx,
+                                   proj[:, g0:g0 + nh] if self.head_gate else None)
+        return LazyLinear(o, self.w_o, self.b_o)

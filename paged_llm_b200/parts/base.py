@@ -37,9 +37,10 @@ class PartSpec:
 
 @dataclass
 class LayerSpec:
-    """One layer: how mixer, feed-forward and norms are arranged (`block`)."""
+    """One layer: how mixer, feed-forward and norms are arranged (`block`: the registry key of the arrangement,
+    or a `PartSpec` if the arrangement has parameters and tensors of its own)."""
 
-    block: str
+    block: "str | PartSpec"
     mixer: PartSpec
     feed_forward: PartSpec | None          # None: the layer has no feed-forward
     norms: dict[str, PartSpec]
@@ -80,7 +81,7 @@ class TensorSpec:
     weights and the like: a tensor stored in 32-bit stays 32-bit, else compute
     dtype), "table_int" (integer tables: int32).
     init: how the random-weights mode draws it: "normal", "norm" (1 or 1+noise), "norm_zero" (0 or noise:
-    a norm weight stored as its deviation from 1).
+    a norm weight stored as its deviation from 1), "identity" (a matrix: the identity, or that plus noise).
     optional: may be absent from the checkpoint (e.g. a tied head).
     shape: an entry of -1 stands for a size that only the checkpoint gives (the rows of a table that
     config.json does not state); `draw_shape` is then what the random-weights mode draws.
@@ -121,6 +122,16 @@ class FixedState:
     dtype: torch.dtype = torch.float32
 
 
+def cache_leaves(requirement) -> list:
+    """The single needs (`PagedKV`, `FixedState`) of a mixer's cache requirement, which may be one need, None, or a
+    tuple of requirements (a mixer made of several mixers: each part gets a view of its own)."""
+    if requirement is None:
+        return []
+    if isinstance(requirement, tuple):
+        return [leaf for r in requirement for leaf in cache_leaves(r)]
+    return [requirement]
+
+
 # --------------------------------------------------------------------------- lazy branch outputs
 
 @dataclass
@@ -130,17 +141,20 @@ class LazyLinear:
     A mixer or feed-forward whose last operation is a projection may return this
     instead of a tensor.  The norm that consumes the branch can then let one
     kernel do projection + residual sum + normalisation; anything else calls
-    `materialize`.  A part that returns a plain tensor works everywhere too."""
+    `materialize`.  A part that returns a plain tensor works everywhere too.
+    `bias` (float32 [out] or None) is added to the product."""
 
     input: torch.Tensor
     weight: torch.Tensor
+    bias: torch.Tensor | None = None
 
     def materialize(self, ops) -> torch.Tensor:
-        return ops.linear(self.input, self.weight)
+        y = ops.linear(self.input, self.weight)
+        return y if self.bias is None else ops.add_bias(y, self.bias)
 
     def rows(self, ops, idx: torch.Tensor) -> "LazyLinear":
         """The same branch for the rows `idx` only."""
-        return LazyLinear(ops.gather_rows(self.input, idx), self.weight)
+        return LazyLinear(ops.gather_rows(self.input, idx), self.weight, self.bias)
 
 
 @dataclass
@@ -158,6 +172,22 @@ class LazyNormed:
     def rows(self, ops, idx: torch.Tensor) -> "LazyNormed":
         b = self.branch
         return LazyNormed(b.rows(ops, idx) if hasattr(b, "rows") else ops.gather_rows(b, idx), self.norm)
+
+
+@dataclass
+class StreamBranch:
+    """A branch output that several copies of the residual stream are waiting for (hyper-connections): the copies
+    become x_t <- sum_s mix[s, t] x_s + out[t] * branch, all at once from the old ones.  `mix` [streams, streams]
+    and `out` [streams] are float32 tensors on the device; `branch` is a tensor or a `LazyLinear`.  The norm that
+    follows carries the update out in the kernel that also forms its own input."""
+
+    branch: object
+    mix: torch.Tensor
+    out: torch.Tensor
+
+    def rows(self, ops, idx: torch.Tensor) -> "StreamBranch":
+        b = self.branch
+        return StreamBranch(b.rows(ops, idx) if hasattr(b, "rows") else ops.gather_rows(b, idx), self.mix, self.out)
 
 
 def materialize(branch, ops):
@@ -231,7 +261,9 @@ class Head(Part):
 class Mixer(Part):
     """Mixes information between the tokens of a request (attention here)."""
 
-    def cache_requirement(self) -> PagedKV | FixedState | None:
+    def cache_requirement(self) -> "PagedKV | FixedState | tuple | None":
+        """What the mixer keeps per request: pages of keys and values, a state of fixed size, nothing, or, for a
+        mixer made of several, a tuple with the requirement of each part (`cache.parts` holds their views)."""
         return None
 
     def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:

@@ -6,7 +6,9 @@ x += mixer(norm_in(x)) alone."""
 
 from __future__ import annotations
 
-from .base import Block, LazyNormed, register_block
+import torch
+
+from .base import Block, LazyNormed, StreamBranch, TensorSpec, materialize, register_block
 
 
 @register_block("pre_norm")
@@ -46,3 +48,55 @@ class SandwichNormBlock(Block):
         if not self.feed_forward.accepts_lazy_input:
             h = ctx.ops.materialize(h)
         return x, LazyNormed(self.feed_forward.forward(h, ctx), self.norms["behind_ffn"])
+
+
+@register_block("hyper_connections")
+class HyperConnectionBlock(Block):
+    """Pre-norm layer over `streams` copies x_1 .. x_s of the residual stream (a row of the stream tensor holds them
+    side by side, [rows, streams * width]).  For sublayer q (the mixer, then the feed-forward) with its learned
+    vectors `in`, `out` [streams] and matrix `mix` [streams, streams] (indexed [from, to]):
+
+        u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix[s, t] x_s + out[t] y   (all t from the old x)
+
+    The update travels as a `StreamBranch` to whatever norm comes next, so that one kernel mixes the copies, adds the
+    branch, forms the next u and norms it.  `weights`: {"mixer": (in, out, mix), "ffn": (in, out, mix)} tensor names."""
+
+    NORM_NAMES = ("input", "post_mixer")
+
+    def __init__(self, mixer, feed_forward, norms, weights: dict, streams: int):
+        super().__init__(mixer, feed_forward, norms)
+        self.streams = int(streams)
+        self.names = {k: tuple(v) for k, v in weights.items() if k == "mixer" or feed_forward is not None}
+        self.hc: dict[str, tuple] = {}
+
+    def tensor_specs(self):
+        out = super().tensor_specs()
+        s = self.streams
+        for w_in, w_out, w_mix in self.names.values():
+            out[w_in] = TensorSpec((s,), role="vector", init="norm")
+            out[w_out] = TensorSpec((s,), role="vector", init="norm")
+            out[w_mix] = TensorSpec((s, s), role="vector", init="identity")
+        return out
+
+    def load(self, tensors):
+        super().load(tensors)
+        for key, names in self.names.items():
+            self.hc[key] = tuple(tensors[n].float().contiguous() for n in names)
+
+    def _sublayer(self, key, norm, part, x, pending, ctx, *args):
+        ops = ctx.ops
+        w_in, w_out, w_mix = self.hc[key]
+        if pending is None:
+            h = ops.stream_norm(x, self.streams, None, None, None, w_in, norm.weight, norm.groups, norm.eps)
+        elif isinstance(pending, StreamBranch):
+            h = ops.stream_norm(x, self.streams, materialize(pending.branch, ops), pending.mix, pending.out, w_in,
+                                norm.weight, norm.groups, norm.eps)
+        else:
+            raise TypeError("a layer of several streams follows a layer of one")
+        return StreamBranch(part.forward(h, ctx, *args), w_mix, w_out)
+
+    def forward(self, x, pending, ctx, cache):
+        pending = self._sublayer("mixer", self.norms["input"], self.mixer, x, pending, ctx, cache)
+        if self.feed_forward is not None:
+            pending = self._sublayer("ffn", self.norms["post_mixer"], self.feed_forward, x, pending, ctx)
+        return x, pending

@@ -13,8 +13,9 @@ from .base import Embedding, Head, TensorSpec, register_embedding, register_head
 
 @register_embedding("embedding")
 class TokenEmbedding(Embedding):
-    def __init__(self, weights: dict[str, str], vocab_size: int, hidden_size: int, scale: float = 1.0):
+    def __init__(self, weights: dict[str, str], vocab_size: int, hidden_size: int, scale: float = 1.0, streams: int = 1):
         self.vocab_size, self.hidden_size, self.scale = vocab_size, hidden_size, float(scale)
+        self.streams = int(streams)       # copies of the row laid side by side (a model of several residual streams)
         self.name = weights["weight"]
         self.weight = None
 
@@ -25,6 +26,8 @@ class TokenEmbedding(Embedding):
         self.weight = tensors[self.name].contiguous()
 
     def forward(self, ids, ctx):
+        if self.streams > 1:
+            return ctx.ops.embedding(self.weight, ids, self.scale, copies=self.streams)
         if self.scale != 1.0:
             return ctx.ops.embedding(self.weight, ids, self.scale)      # (the stream is float32: the product is too)
         return ctx.ops.embedding(self.weight, ids)

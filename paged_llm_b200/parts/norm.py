@@ -2,19 +2,27 @@
 root, the weight multiplied before the down-cast (reference:
 pagedllm/model/llama.py:74-83).  With `unit_offset` the checkpoint stores the
 weight around zero and the factor is 1 + w; it is formed once, in float32, when
-the weights are taken."""
+the weights are taken.
+
+`groups` g > 1: the row is cut into g equal consecutive parts and each part is divided by its own root mean
+square (the weight still spans the row).  `streams` s > 1: the residual stream arrives as s copies per token
+([rows, s * dim], hyper-connections); the norm sees their sum, after a pending `StreamBranch` has been mixed in."""
 
 from __future__ import annotations
 
 import torch
 
-from .base import LazyLinear, LazyNormed, Norm, TensorSpec, materialize, register_norm
+from .base import LazyLinear, LazyNormed, Norm, StreamBranch, TensorSpec, materialize, register_norm
 
 
 @register_norm("rms_norm")
 class RMSNorm(Norm):
-    def __init__(self, weights: dict[str, str], dim: int, eps: float, unit_offset: bool = False):
+    def __init__(self, weights: dict[str, str], dim: int, eps: float, unit_offset: bool = False, groups: int = 1,
+                 streams: int = 1):
         self.dim, self.eps, self.unit_offset = dim, float(eps), bool(unit_offset)
+        if groups < 1 or dim % groups:
+            raise ValueError(f"a norm over {dim} values does not divide into {groups} equal parts")
+        self.groups, self.streams = int(groups), int(streams)
         self.name = weights["weight"]
         self.weight = None
 
@@ -29,11 +37,21 @@ class RMSNorm(Norm):
         return self.weight.numel() * self.weight.element_size()
 
     def forward(self, x, ctx):
-        return ctx.ops.rms_norm(x, self.weight, self.eps)
+        return self.add_forward(x, None, ctx)
 
     def add_forward(self, x, branch, ctx):
+        if self.groups > 1 or self.streams > 1 or isinstance(branch, StreamBranch):
+            # one kernel: the copies of the stream take the branch in, are summed, and the sum is normed in parts
+            ops = ctx.ops
+            if isinstance(branch, StreamBranch):
+                return ops.stream_norm(x, self.streams, materialize(branch.branch, ops), branch.mix, branch.out, None,
+                                       self.weight, self.groups, self.eps)
+            y = materialize(branch, ops) if branch is not None else None
+            return ops.stream_norm(x, self.streams, y, None, None, None, self.weight, self.groups, self.eps)
         if branch is None:
             return ctx.ops.rms_norm(x, self.weight, self.eps)
+        if isinstance(branch, LazyLinear) and branch.bias is not None:
+            branch = branch.materialize(ctx.ops)
         if isinstance(branch, LazyLinear):
             return ctx.ops.linear_add_rms_norm(branch.input, branch.weight, x, self.weight, self.eps)
         return ctx.ops.add_rms_norm(x, branch, self.weight, self.eps)

@@ -1,0 +1,59 @@
+"""Two mixers side by side on the same input: out = left_scale * left(h) + right_scale * right(h).
+
+The parts are ordinary mixers named by registry key; each keeps whatever it keeps (pages of keys and values, a state
+of fixed size, nothing), so the cache requirement is the pair of theirs and each part gets its own view
+(`cache.parts`).  The weighted sum of the two branch outputs, with a bias either output projection may have, is
+float32 and is formed by one kernel.
+"""
+
+from __future__ import annotations
+
+from .base import MIXERS, LazyLinear, Mixer, PartSpec, make_part, register_mixer
+
+
+@register_mixer("parallel")
+class ParallelMixer(Mixer):
+    accepts_lazy_input = False
+
+    def __init__(self, weights: dict[str, str], left: PartSpec, right: PartSpec, left_scale: float = 1.0,
+                 right_scale: float = 1.0):
+        self.parts = (make_part(MIXERS, "mixer", left), make_part(MIXERS, "mixer", right))
+        self.scales = (float(left_scale), float(right_scale))
+
+    @property
+    def capturable(self):
+        return all(p.capturable for p in self.parts)
+
+    def cache_requirement(self):
+        return tuple(p.cache_requirement() for p in self.parts)
+
+    def attention_plan_key(self):
+        keys = {k for k in (getattr(p, "attention_plan_key", lambda: None)() for p in self.parts) if k is not None}
+        if len(keys) > 1:
+            raise ValueError(f"the two parts of a parallel mixer plan attention differently: {sorted(keys)}")
+        return next(iter(keys), None)
+
+    def tensor_specs(self):
+        out = {}
+        for p in self.parts:
+            out.update(p.tensor_specs())
+        return out
+
+    def load(self, tensors):
+        for p in self.parts:
+            p.load(tensors)
+
+    def bytes_read_per_step(self):
+        return sum(p.bytes_read_per_step() for p in self.parts)
+
+    def forward(self, h, ctx, cache):
+        ops = ctx.ops
+        outs = []
+        for part, view in zip(self.parts, cache.parts):
+            y = part.forward(h, ctx, view)
+            bias = None
+            if isinstance(y, LazyLinear):
+                y, bias = ops.linear(y.input, y.weight), y.bias
+            outs.append((y, bias))
+        (a, bias_a), (b, bias_b) = outs
+        return ops.scaled_sum(a, self.scales[0], bias_a, b, self.scales[1], bias_b)

@@ -47,8 +47,11 @@ def random_tensors(config: ModelConfig, seed: int = 0, std: float = 0.02, norm_s
         if spec.role == "table_int":
             raise NotImplementedError(f"{name}: random integer tables are not defined")
         shape = spec.draw_shape or spec.shape
-        if spec.init in ("norm", "norm_zero"):        # norm weights: around one, or (stored as a deviation) around zero
+        if spec.init in ("norm", "norm_zero", "identity"):
+            # norm weights: around one, or (stored as a deviation) around zero; a mixing matrix: around the identity
             t = torch.full(shape, 1.0 if spec.init == "norm" else 0.0, dtype=torch.float32)
+            if spec.init == "identity":
+                t = torch.eye(shape[0], shape[1], dtype=torch.float32)
             if norm_std:
                 t = t + norm_std * torch.randn(shape, generator=gen, dtype=torch.float32)
         else:
@@ -118,13 +121,15 @@ def draw_on_device(expected: dict, stub: dict, compute: torch.dtype, device, ops
         if spec.role == "table_int":
             raise NotImplementedError(f"{name}: random integer tables are not defined")
         shape = spec.draw_shape or spec.shape
-        if spec.init in ("norm", "norm_zero"):
+        if spec.init in ("norm", "norm_zero", "identity"):
             centre = 1.0 if spec.init == "norm" else 0.0
             t = torch.empty(shape, dtype=torch.float32, device=device)
             if stub["norm_std"]:
                 ops.fill_normal(t, stub["seed"], tensor_key(name), centre, stub["norm_std"])
             else:
                 t.fill_(centre)
+            if spec.init == "identity":
+                t += torch.eye(shape[0], shape[1], dtype=torch.float32, device=device)
         else:
             t = torch.empty(shape, dtype=compute, device=device)
             ops.fill_normal(t, stub["seed"], tensor_key(name), 0.0, stub["std"])

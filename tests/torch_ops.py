@@ -29,9 +29,47 @@ class TorchOps:
         self.compute_dtype = dtype
 
     # ---- elementwise / norms ---------------------------------------------------
-    def embedding(self, table, ids, scale=1.0):
+    def embedding(self, table, ids, scale=1.0, copies=1):
         self._count("embedding")
-        return table[ids.long()].float() * scale
+        return (table[ids.long()].float() * scale).repeat(1, copies)
+
+    def stream_norm(self, x, streams, branch, mix, out, w_in, norm_w, groups, eps):
+        self._count("stream_norm")
+        rows, width = x.shape[0], x.shape[1] // streams
+        xs = x.view(rows, streams, width)
+        if branch is not None:
+            y = branch.float()
+            if mix is None:
+                xs += y[:, None, :]
+            else:
+                xs.copy_(torch.einsum("st,rsw->rtw", mix.float(), xs) + out.float()[None, :, None] * y[:, None, :])
+        u = xs.sum(1) if w_in is None else torch.einsum("s,rsw->rw", w_in.float(), xs)
+        p = u.view(rows, groups, width // groups)
+        p = p * torch.rsqrt((p * p).mean(-1, keepdim=True) + eps)
+        return (p.reshape(rows, width) * norm_w.float()).to(self.compute_dtype)
+
+    def poly_norm(self, z, coef, eps):
+        self._count("poly_norm")
+        z = z.float()
+
+        def unit(t):
+            return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + eps)
+
+        a, b, c, e = coef.float()
+        return (a * unit(z) + b * unit(z * z) + c * unit(z * z * z) + e).to(self.compute_dtype)
+
+    def add_bias(self, y, bias):
+        y += bias.to(y.dtype)
+        return y
+
+    def scaled_sum(self, a, scale_a, bias_a, b, scale_b, bias_b):
+        self._count("scaled_sum")
+        a, b = a.float(), b.float()
+        if bias_a is not None:
+            a = a + bias_a
+        if bias_b is not None:
+            b = b + bias_b
+        return scale_a * a + scale_b * b
 
     def dyt(self, x, branch, post, pre, out_dtype=None):
         self._count("dyt")
@@ -224,11 +262,130 @@ class TorchOps:
             kv[page, 0, :, p % ps, :] = k[t].to(kv.dtype)
             kv[page, 1, :, p % ps, :] = v[t].to(kv.dtype)
 
-    def heads_linear(self, x, col0, head_stride, w):
+    def heads_linear(self, x, col0, head_stride, w, out_float32=False):
         self._count("heads_linear")
         nh, N, K = w.shape
         xs = torch.stack([x[:, col0 + h * head_stride:col0 + h * head_stride + K] for h in range(nh)], dim=1).float()
-        return torch.einsum("thk,hnk->thn", xs, w.float()).reshape(x.shape[0], nh * N).to(self.compute_dtype)
+        y = torch.einsum("thk,hnk->thn", xs, w.float()).reshape(x.shape[0], nh * N)
+        return y if out_float32 else y.to(self.compute_dtype)
+
+    @staticmethod
+    def _turn(x, position, pos, back=False):
+        """x [T, heads, n]: the first rotary_dim elements of each head turned by the table's angles at `pos`
+        (`back`: by minus those angles), pairs as the table says."""
+        rd = position.rotary_dim
+        cs = position.table[pos]                            # [T, rd/2, 2]
+        cos, sin = cs[..., 0][:, None, :], cs[..., 1][:, None, :]
+        if back:
+            sin = -sin
+        out = x.clone()
+        if position.pairing == "half":
+            a, b = x[..., :rd // 2], x[..., rd // 2:rd]
+            out[..., :rd // 2], out[..., rd // 2:rd] = a * cos - b * sin, b * cos + a * sin
+        else:
+            a, b = x[..., 0:rd:2], x[..., 1:rd:2]
+            out[..., 0:rd:2], out[..., 1:rd:2] = a * cos - b * sin, b * cos + a * sin
+        return out
+
+    def rotated_qkv_write(self, proj, bias, nh, nkv, d, dv, D, position, value_position, ctx, kv, block_table, write=True):
+        self._count("rotated_qkv_write")
+        T = proj.shape[0]
+        n = nh * d + nkv * (d + dv)
+        pf = proj[:, :n].float()
+        if bias is not None:
+            pf = pf + bias.float()
+        pos = ctx.positions.long()
+        q = pf[:, :nh * d].view(T, nh, d)
+        k = pf[:, nh * d:(nh + nkv) * d].view(T, nkv, d)
+        v = pf[:, (nh + nkv) * d:].view(T, nkv, dv)
+        if position is not None:
+            q, k = self._turn(q, position, pos), self._turn(k, position, pos)
+        if value_position is not None:
+            v = self._turn(v, value_position, pos)
+        qp = torch.zeros(T, nh, D)
+        qp[:, :, :d] = q
+        if write:
+            kp, vp = torch.zeros(T, nkv, D), torch.zeros(T, nkv, D)
+            kp[:, :, :d], vp[:, :, :dv] = k, v
+            self._write_slots(ctx, kv, block_table, kp, vp)
+        return qp.reshape(T, nh * D).to(self.compute_dtype)
+
+    def head_unrotate_gate(self, o, nh, D, dv, value_position, ctx, gate=None):
+        self._count("head_unrotate_gate")
+        T = o.shape[0]
+        out = o.float().view(T, nh, D)[:, :, :dv]
+        if value_position is not None:
+            out = self._turn(out, value_position, ctx.positions.long(), back=True)
+        if gate is not None:
+            out = out * torch.sigmoid(gate.float())[:, :, None]
+        return out.reshape(T, nh * dv).to(self.compute_dtype)
+
+    def causal_conv(self, yx, col0, C, b_in, conv_w, conv_b, state, ctx):
+        self._count("causal_conv")
+        taps = conv_w.shape[1]
+        hist = taps - 1
+        x = yx[:, col0:col0 + C].float() + b_in[col0:col0 + C]
+        out = torch.zeros(yx.shape[0], C)
+        cu = ctx.host.cu
+        for s, slot in enumerate(ctx.host.state_slots):
+            assert slot >= 0, "a request of a model with state must own a slot"
+            nq = cu[s + 1] - cu[s]
+            seq = torch.cat([state[slot][:hist * C].view(hist, C), x[cu[s]:cu[s + 1]]], dim=0)
+            u = conv_b[None, :].expand(nq, C).clone()
+            for j in range(taps):
+                u = u + seq[j:j + nq] * conv_w[:, j][None, :]
+            out[cu[s]:cu[s + 1]] = u
+        low = out.to(self.compute_dtype)
+        return out, (out if low.dtype == torch.float32 else low)
+
+    def gated_recurrence(self, gates, b_gates, u, yx, b_in, rate, blocks, taps, state, ctx):
+        self._count("gated_recurrence")
+        T, C = u.shape
+        bw, hist = C // blocks, taps - 1
+        g = gates.view(T, blocks, 2 * bw) + b_gates[None]
+        r = torch.sigmoid(g[:, :, :bw]).reshape(T, C)
+        i = torch.sigmoid(g[:, :, bw:]).reshape(T, C)
+        a = torch.exp(rate[None, :] * r)
+        drive = torch.sqrt(1.0 - a * a) * i * u
+        y = torch.nn.functional.gelu(yx[:, :C].float() + b_in[:C], approximate="tanh")
+        x = yx[:, C:2 * C].float() + b_in[C:]
+        out = torch.zeros(T, C)
+        cu = ctx.host.cu
+        for s, slot in enumerate(ctx.host.state_slots):
+            st = state[slot]
+            S = st[hist * C:]
+            for t in range(cu[s], cu[s + 1]):
+                S.mul_(a[t]).add_(drive[t])
+                out[t] = S * y[t]
+            old = st[:hist * C].view(hist, C)
+            old.copy_(torch.cat([old, x[cu[s]:cu[s + 1]]], dim=0)[-hist:].clone() if hist else old)
+        return out.to(self.compute_dtype)
+
+    def linear_attention_scan(self, proj, z, z_bias, H, d, dv, tau, q_scale, state, ctx):
+        self._count("linear_attention_scan")
+        T = proj.shape[0]
+        pf = proj.float()
+        q = pf[:, :H * d].view(T, H, d) * q_scale
+        k = pf[:, H * d:2 * H * d].view(T, H, d)
+        v = pf[:, 2 * H * d:2 * H * d + H * dv].view(T, H, dv)
+        alpha = torch.exp(torch.nn.functional.logsigmoid(z.float() + z_bias) / tau).view(T, H, d)
+        out = torch.zeros(T, H * dv)
+        cu = ctx.host.cu
+        for s, slot in enumerate(ctx.host.state_slots):
+            assert slot >= 0, "a request of a model with state must own a slot"
+            S = state[slot].view(H, dv, d)
+            for t in range(cu[s], cu[s + 1]):
+                S.mul_(alpha[t][:, None, :]).add_(v[t][:, :, None] * k[t][:, None, :])
+                out[t] = torch.einsum("hvd,hd->hv", S, q[t]).reshape(H * dv)
+        return out
+
+    def head_norm_gate(self, o, proj, g_col0, H, dv, norm_w, eps):
+        self._count("head_norm_gate")
+        T = o.shape[0]
+        v = o.view(T, H, dv)
+        v = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps) * norm_w[None, None, :]
+        g = proj[:, g_col0:g_col0 + H * dv].float()
+        return (v.reshape(T, H * dv) * (g * torch.sigmoid(g))).to(self.compute_dtype)
 
     def normed_qkv_write(self, proj, nh, nkv, d, dv, D, q_weight, k_weight, eps, ctx, kv, block_table, has_kv=True,
                          write=True):
