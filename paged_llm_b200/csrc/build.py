@@ -43,6 +43,10 @@ MODULES: dict[str, list[str]] = {
     "moe": ["common.cu", "moe.cu"],
     # state-space mixer (short convolution, recurrence, gated norm in parts)
     "ssm": ["common.cu", "ssm.cu"],
+    # several copies of the residual stream, norms in parts, PolyNorm
+    "streams": ["common.cu", "streams.cu"],
+    # convolution with a gated recurrence per channel; gated linear attention
+    "recurrent": ["common.cu", "recurrent.cu"],
 }
 
 

@@ -456,3 +456,145 @@ PL_EXPORT int pl_latent_q(const void* q_abs, const void* q, int dtype, int T, vo
     PL_LAUNCHED("latent_q");
     return 0;
 }
+
+// ------------------------------------------------------------------ attention whose values are rotated too
+// A head of n elements turned by the angles of one table row `cs` [rd / 2] of (cos, sin): element e < rd is paired
+// with e ^ 1 (interleaved) or with e +- rd / 2 (halves), elements from rd on pass.  `dir` = -1 turns back.
+// `elem(i)` gives element i of the head before the turn.
+template <typename F>
+__device__ __forceinline__ float turned(const float2* cs, int rd, int inter, float dir, int e, F elem) {
+    const float self = elem(e);
+    if (cs == nullptr || e >= rd) return self;
+    const int half = rd >> 1;
+    int i, partner;
+    bool second;
+    if (inter) {
+        i = e >> 1, partner = e ^ 1, second = e & 1;
+    } else {
+        second = e >= half, i = second ? e - half : e, partner = second ? e - half : e + half;
+    }
+    const float2 t = cs[i];
+    const float sn = dir * t.y, other = elem(partner);
+    return second ? fmaf(self, t.x, other * sn) : fmaf(self, t.x, -other * sn);
+}
+
+// proj row: [q: nh*d | k: nkv*d | v: nkv*dv | ...] with `bias` (float32, the same layout, may be null) added first.
+// q and k are turned by the token's position with the table `qk` (rd_qk elements of each head), v with the table
+// `vt` over rd_v elements.  Q out: [T, nh*D], head h at h*D, columns d..D zero; K and V go to the token's page slot,
+// padded to D with zeros.  One block per token.
+struct RotTable {
+    const float2* table;    // [len, rd / 2] or null: no rotation
+    int len, rd, inter;
+};
+
+template <typename T>
+__global__ void rotated_qkv_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ bias, T* __restrict__ q_out,
+                                   T* __restrict__ kv, SlotArgs sa, RotTable qk, RotTable vt, int nh, int nkv, int d, int dv,
+                                   int D, int write) {
+    const int t = blockIdx.x;
+    const int s = sa.token_seq[t];
+    T* qo = q_out + (size_t)t * nh * D;
+    if (s < 0) {                                   // a row that pads the step
+        for (int i = threadIdx.x; i < nh * D; i += blockDim.x) qo[i] = from_float<T>(0.f);
+        return;
+    }
+    const int pos = sa.positions[t];
+    const T* row = proj + (size_t)t * ld;
+    const float2* cs_qk = qk.table != nullptr && pos >= 0 && pos < qk.len ? qk.table + (size_t)pos * (qk.rd >> 1) : nullptr;
+    const float2* cs_v = vt.table != nullptr && pos >= 0 && pos < vt.len ? vt.table + (size_t)pos * (vt.rd >> 1) : nullptr;
+    for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+        const int h = i / D, c = i - h * D;
+        float v = 0.f;
+        if (c < d) {
+            const int base = h * d;
+            v = turned(cs_qk, qk.rd, qk.inter, 1.f, c,
+                       [&](int e) { return to_float(row[base + e]) + (bias != nullptr ? __ldg(bias + base + e) : 0.f); });
+        }
+        qo[i] = from_float<T>(v);
+    }
+    if (!write) return;
+    const long long slot = key_slot(sa, t, s, pos, nkv, D);
+    if (slot < 0) return;
+    const size_t head_stride = (size_t)sa.ps * D, v_off = (size_t)nkv * sa.ps * D;
+    const int k0 = nh * d, v0 = nh * d + nkv * d;
+    for (int i = threadIdx.x; i < nkv * D; i += blockDim.x) {
+        const int h = i / D, c = i - h * D;
+        float kk = 0.f, vv = 0.f;
+        if (c < d) {
+            const int base = k0 + h * d;
+            kk = turned(cs_qk, qk.rd, qk.inter, 1.f, c,
+                        [&](int e) { return to_float(row[base + e]) + (bias != nullptr ? __ldg(bias + base + e) : 0.f); });
+        }
+        if (c < dv) {
+            const int base = v0 + h * dv;
+            vv = turned(cs_v, vt.rd, vt.inter, 1.f, c,
+                        [&](int e) { return to_float(row[base + e]) + (bias != nullptr ? __ldg(bias + base + e) : 0.f); });
+        }
+        kv[slot + h * head_stride + c] = from_float<T>(kk);
+        kv[slot + v_off + h * head_stride + c] = from_float<T>(vv);
+    }
+}
+
+PL_EXPORT int pl_rotated_qkv_write(const void* proj, int dtype, int T, int ld, const float* bias, void* q_out, void* kv,
+                                   const int* positions, const int* token_seq, const int* block_table, int bt_stride,
+                                   int num_pages, int ps, const float* qk_table, int qk_len, int qk_rd, int qk_inter,
+                                   const float* v_table, int v_len, int v_rd, int v_inter, int nh, int nkv, int d, int dv,
+                                   int D, int write, cudaStream_t stream) {
+    if (T == 0) return 0;
+    PL_REQUIRE(nh > 0 && nkv > 0 && d > 0 && dv > 0 && D >= d && D >= dv, "rotated_qkv_write: bad head sizes d=%d dv=%d D=%d", d,
+               dv, D);
+    PL_REQUIRE(qk_rd % 2 == 0 && qk_rd <= d && v_rd % 2 == 0 && v_rd <= dv, "rotated_qkv_write: rotation of %d / %d elements of "
+               "heads of %d / %d", qk_rd, v_rd, d, dv);
+    SlotArgs sa{positions, token_seq, block_table, bt_stride, num_pages, ps};
+    RotTable qk{(const float2*)qk_table, qk_len, qk_rd, qk_inter}, vt{(const float2*)v_table, v_len, v_rd, v_inter};
+    if (dtype == PL_F32)
+        rotated_qkv_kernel<float><<<T, 256, 0, stream>>>((const float*)proj, ld, bias, (float*)q_out, (float*)kv, sa, qk, vt, nh,
+                                                         nkv, d, dv, D, write);
+    else if (dtype == PL_BF16)
+        rotated_qkv_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)proj, ld, bias, (__nv_bfloat16*)q_out,
+                                                                 (__nv_bfloat16*)kv, sa, qk, vt, nh, nkv, d, dv, D, write);
+    else
+        return pl_fail("rotated_qkv_write: unknown dtype %d", dtype);
+    PL_LAUNCHED("rotated_qkv_write");
+    return 0;
+}
+
+// out[t, h*dv + c] = turn_back(o[t, h*D + ..dv], position of t)[c] * sigmoid(gate[t, h]): each head's output (the
+// weighted sum of values that were rotated by their own positions) is turned by minus the query's position, then
+// gated by one number per head.  `gate` [T, nh] with row stride ldg, or null.
+template <typename T>
+__global__ void head_unrotate_gate_kernel(const T* __restrict__ o, int D, const T* __restrict__ gate, int ldg,
+                                          const int* __restrict__ positions, const int* __restrict__ token_seq, RotTable vt,
+                                          T* __restrict__ out, int nh, int dv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const bool real = token_seq[t] >= 0;
+    const float2* cs = real && vt.table != nullptr && pos >= 0 && pos < vt.len ? vt.table + (size_t)pos * (vt.rd >> 1) : nullptr;
+    const T* orow = o + (size_t)t * nh * D;
+    for (int i = threadIdx.x; i < nh * dv; i += blockDim.x) {
+        const int h = i / dv, c = i - h * dv;
+        float v = turned(cs, vt.rd, vt.inter, -1.f, c, [&](int e) { return to_float(orow[h * D + e]); });
+        if (gate != nullptr) v *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * ldg + h])));
+        out[(size_t)t * nh * dv + i] = from_float<T>(v);
+    }
+}
+
+PL_EXPORT int pl_head_unrotate_gate(const void* o, int dtype, int T, int D, const void* gate, int ldg, const int* positions,
+                                    const int* token_seq, const float* v_table, int v_len, int v_rd, int v_inter, void* out,
+                                    int nh, int dv, cudaStream_t stream) {
+    if (T == 0) return 0;
+    PL_REQUIRE(nh > 0 && dv > 0 && D >= dv && v_rd % 2 == 0 && v_rd <= dv, "head_unrotate_gate: bad sizes dv=%d D=%d rd=%d", dv, D,
+               v_rd);
+    RotTable vt{(const float2*)v_table, v_len, v_rd, v_inter};
+    if (dtype == PL_F32)
+        PL_CUDA(launch_pdl(head_unrotate_gate_kernel<float>, dim3(T), dim3(256), 0, stream, (const float*)o, D, (const float*)gate,
+                           ldg, positions, token_seq, vt, (float*)out, nh, dv));
+    else if (dtype == PL_BF16)
+        PL_CUDA(launch_pdl(head_unrotate_gate_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16*)o, D,
+                           (const __nv_bfloat16*)gate, ldg, positions, token_seq, vt, (__nv_bfloat16*)out, nh, dv));
+    else
+        return pl_fail("head_unrotate_gate: unknown dtype %d", dtype);
+    return 0;
+}

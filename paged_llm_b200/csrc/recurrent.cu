@@ -1,0 +1,339 @@
+// Mixers that carry a state of fixed size from token to token, in float32:
+//
+//  * a causal convolution per channel over a projection's columns (bias on the input, bias on the output, no
+//    activation), whose last taps-1 inputs are part of the request's state;
+//  * a real-gated linear recurrence per channel:
+//        a = exp(rate * sigmoid(g_r)),   S_t = a S_(t-1) + sqrt(1 - a^2) * sigmoid(g_i) * u_t,   out = S_t * gelu_tanh(y_t)
+//  * gated linear attention, a matrix state per head with a decay per key channel:
+//        alpha = exp(log_sigmoid(z) / tau),   S_t = diag(alpha_t) S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t
+//  * the norm of each head's output over its value size, times silu(gate).
+//
+// Every request of the step brings its next tokens (one when it decodes, many in a prompt portion); its state lives
+// in a slot of [slots, state_stride] floats.  The recurrences run in the order of the tokens with a fixed order of
+// sums, so what a position gets does not depend on how the prompt was cut or on the batch.
+#include "common.cuh"
+
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+// log(sigmoid(v)) without overflow: min(v, 0) - log1p(exp(-|v|))
+__device__ __forceinline__ float log_sigmoid_f(float v) { return fminf(v, 0.f) - log1pf(expf(-fabsf(v))); }
+
+// ------------------------------------------------------------------ causal convolution
+// grid: (requests, channel blocks of 32, token chunks of CONV_TOK).  Input of channel c at token t:
+// in[t, col0 + c] + b_in[col0 + c].  The block of chunk 0 is the only one that reads the request's old inputs (the
+// state's first (taps-1) * C floats, [taps-1][C]), and it alone writes the new ones, after a barrier.
+constexpr int CONV_TOK = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ in, int ld, int col0, int C,
+                                                          const float* __restrict__ b_in, const float* __restrict__ cw,
+                                                          const float* __restrict__ cb, int taps, float* __restrict__ state,
+                                                          long long state_stride, const int* __restrict__ cu_q,
+                                                          const int* __restrict__ slots, float* __restrict__ u,
+                                                          T* __restrict__ u_low) {
+    const int s = blockIdx.x;
+    const int slot = slots[s];
+    const int q0 = cu_q[s], nq = cu_q[s + 1] - q0;
+    const int t_lo = blockIdx.z * CONV_TOK, t_hi = min(nq, t_lo + CONV_TOK);
+    if (slot < 0 || t_lo >= nq) return;
+    const int lane_c = threadIdx.x & 31, lane_t = threadIdx.x >> 5;
+    const int c = blockIdx.y * 32 + lane_c;
+    const bool ok = c < C;
+    float* st = state + (size_t)slot * state_stride;
+    const int hist = taps - 1;
+    const float bi = ok ? __ldg(b_in + col0 + c) : 0.f;
+    const T* col = in + (size_t)q0 * ld + col0 + (ok ? c : 0);
+    auto input = [&](int src) { return src >= 0 ? to_float(col[(size_t)src * ld]) + bi : st[(size_t)(hist + src) * C + c]; };
+    if (ok) {
+        const float bias = __ldg(cb + c);
+        for (int t = t_lo + lane_t; t < t_hi; t += 8) {
+            float acc = bias;
+            for (int k = 0; k < taps; ++k) acc = fmaf(__ldg(cw + (size_t)c * taps + k), input(t - hist + k), acc);
+            u[(size_t)(q0 + t) * C + c] = acc;
+            if (u_low != nullptr) u_low[(size_t)(q0 + t) * C + c] = from_float<T>(acc);
+        }
+    }
+    if (blockIdx.z != 0) return;
+    __syncthreads();                                                // every read of the old inputs is done
+    if (ok && lane_t == 0) {
+        // the last taps-1 inputs of [old inputs ; this step's inputs]: in place from the front, since entry j
+        // reads old entry j + nq > j or a new input
+        for (int j = 0; j < hist; ++j) {
+            const int src = nq + j - hist;
+            st[(size_t)j * C + c] = src >= 0 ? to_float(col[(size_t)src * ld]) + bi : st[(size_t)(j + nq) * C + c];
+        }
+    }
+}
+
+// `max_tokens`: no request of the step brings more.  u: [T, C] float32; u_low: the same in `dtype`, or null.
+PL_EXPORT int pl_causal_conv(const void* in, int dtype, int ld, int col0, int C, const float* b_in, const float* cw,
+                             const float* cb, int taps, float* state, long long state_stride, const int* cu_q,
+                             const int* slots, int num_seqs, int max_tokens, float* u, void* u_low, cudaStream_t stream) {
+    if (num_seqs == 0) return 0;
+    PL_REQUIRE(C > 0 && taps >= 1 && taps <= CONV_TOK && max_tokens >= 1 && col0 >= 0 && col0 + C <= ld,
+               "causal_conv: bad sizes C=%d taps=%d col0=%d ld=%d", C, taps, col0, ld);
+    const dim3 grid(num_seqs, (C + 31) / 32, (max_tokens + CONV_TOK - 1) / CONV_TOK);
+    PL_REQUIRE(grid.z <= 65535 && grid.y <= 65535, "causal_conv: %d tokens, %d channels in a step", max_tokens, C);
+    if (dtype == PL_F32)
+        causal_conv_kernel<float><<<grid, 256, 0, stream>>>((const float*)in, ld, col0, C, b_in, cw, cb, taps, state, state_stride,
+                                                            cu_q, slots, u, (float*)u_low);
+    else if (dtype == PL_BF16)
+        causal_conv_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, ld, col0, C, b_in, cw, cb, taps,
+                                                                    state, state_stride, cu_q, slots, u, (__nv_bfloat16*)u_low);
+    else
+        return pl_fail("causal_conv: unknown dtype %d", dtype);
+    PL_LAUNCHED("causal_conv");
+    return 0;
+}
+
+// ------------------------------------------------------------------ real-gated linear recurrence
+// grid: (requests, channel blocks).  Threads: CH = 256 / TL channel lanes x TL token lanes.  A tile of TL * SEG
+// tokens is worked on at once: token lane j takes SEG consecutive tokens, forms their decays a and drives
+// b = sqrt(1 - a^2) * sigmoid(g_i) * u (kept in registers) and the pair (A, B) that carries a state across its
+// tokens (S -> A S + B); the pairs of the lanes in front, applied in order to the state at the start of the tile,
+// give the lane its own start, from which it runs its tokens again and writes S_t * gelu_tanh(y_t + bias).
+// gates: [T, blocks * 2 * bw] float32, per block [recurrence gate: bw | input gate: bw], biases `b_gates` the
+// same; channel c belongs to block c / bw.  The state S of a request: `state_off` floats into its slot.
+constexpr int REC_SEG = 8;
+
+template <typename T, int TL>
+__global__ void __launch_bounds__(256) gated_recurrence_kernel(const float* __restrict__ gates, const float* __restrict__ b_gates,
+                                                               const float* __restrict__ u, const T* __restrict__ yx, int ld,
+                                                               const float* __restrict__ b_y, const float* __restrict__ rate,
+                                                               int C, int bw, float* __restrict__ state, long long state_stride,
+                                                               long long state_off, const int* __restrict__ cu_q,
+                                                               const int* __restrict__ slots, T* __restrict__ out) {
+    constexpr int CH = 256 / TL;
+    __shared__ float carry[2][TL][CH];
+    const int s = blockIdx.x;
+    const int slot = slots[s];
+    const int q0 = cu_q[s], nq = cu_q[s + 1] - q0;
+    if (slot < 0 || nq <= 0) return;
+    const int lane_c = threadIdx.x % CH, lane_t = threadIdx.x / CH;
+    const int c = blockIdx.y * CH + lane_c;
+    const bool ok = c < C;
+    const int cc = ok ? c : 0;
+    const int blk = cc / bw, j = cc - blk * bw;
+    const int gr = blk * 2 * bw + j, gi = gr + bw, G = (C / bw) * 2 * bw;
+    const float br = __ldg(b_gates + gr), bi = __ldg(b_gates + gi), rt = __ldg(rate + cc), by = __ldg(b_y + cc);
+    float* sp = state + (size_t)slot * state_stride + state_off + cc;
+    float S0 = ok ? *sp : 0.f;                                      // the state at the start of the tile
+    for (int t0 = 0; t0 < nq; t0 += TL * REC_SEG) {
+        const int ta = t0 + lane_t * REC_SEG;
+        float a[REC_SEG], b[REC_SEG];
+        float A = 1.f, B = 0.f;
+#pragma unroll
+        for (int i = 0; i < REC_SEG; ++i) {
+            a[i] = 1.f, b[i] = 0.f;
+            if (ok && ta + i < nq) {
+                const size_t row = (size_t)(q0 + ta + i);
+                const float r = sigmoid_f(gates[row * G + gr] + br), in = sigmoid_f(gates[row * G + gi] + bi);
+                const float av = expf(rt * r);
+                a[i] = av;
+                b[i] = sqrtf(fmaxf(1.0f - av * av, 0.f)) * in * u[row * C + c];
+            }
+            A *= a[i];
+            B = fmaf(a[i], B, b[i]);
+        }
+        float S = S0;
+        if (TL > 1) {
+            carry[0][lane_t][lane_c] = A;
+            carry[1][lane_t][lane_c] = B;
+            __syncthreads();
+            float Sj = S0;
+#pragma unroll
+            for (int l = 0; l < TL; ++l) {
+                if (l == lane_t) S = Sj;
+                Sj = fmaf(carry[0][l][lane_c], Sj, carry[1][l][lane_c]);
+            }
+            S0 = Sj;                                                // every lane knows the state behind the tile
+            __syncthreads();
+        }
+#pragma unroll
+        for (int i = 0; i < REC_SEG; ++i) {
+            S = fmaf(a[i], S, b[i]);
+            if (ok && ta + i < nq) {
+                const size_t row = (size_t)(q0 + ta + i);
+                out[row * C + c] = from_float<T>(S * gelu_tanh_f(to_float(yx[row * ld + c]) + by));
+            }
+        }
+        if (TL == 1) S0 = S;
+    }
+    if (ok && lane_t == 0) *sp = S0;
+}
+
+// yx: the projection's rows [y: C | ...] with row stride ld in `dtype`; out: [T, C] in `dtype`.
+PL_EXPORT int pl_gated_recurrence(const float* gates, const float* b_gates, const float* u, const void* yx, int dtype, int ld,
+                                  const float* b_y, const float* rate, int C, int blocks, float* state,
+                                  long long state_stride, long long state_off, const int* cu_q, const int* slots,
+                                  int num_seqs, int max_tokens, void* out, cudaStream_t stream) {
+    if (num_seqs == 0) return 0;
+    PL_REQUIRE(C > 0 && blocks > 0 && C % blocks == 0 && ld >= C, "gated_recurrence: bad sizes C=%d blocks=%d ld=%d", C, blocks, ld);
+    const int bw = C / blocks;
+    const bool few = max_tokens <= 2 * REC_SEG;
+    const int CH = few ? 256 : 32;
+    const dim3 grid(num_seqs, (C + CH - 1) / CH);
+    PL_REQUIRE(grid.y <= 65535, "gated_recurrence: %d channels", C);
+#define PL_REC(TT, L)                                                                                                      \
+    gated_recurrence_kernel<TT, L><<<grid, 256, 0, stream>>>(gates, b_gates, u, (const TT*)yx, ld, b_y, rate, C, bw, state, \
+                                                             state_stride, state_off, cu_q, slots, (TT*)out)
+    if (dtype == PL_F32) {
+        if (few) PL_REC(float, 1); else PL_REC(float, 8);
+    } else if (dtype == PL_BF16) {
+        if (few) PL_REC(__nv_bfloat16, 1); else PL_REC(__nv_bfloat16, 8);
+    } else {
+        return pl_fail("gated_recurrence: unknown dtype %d", dtype);
+    }
+#undef PL_REC
+    PL_LAUNCHED("gated_recurrence");
+    return 0;
+}
+
+// ------------------------------------------------------------------ gated linear attention, the recurrence
+// grid: (requests, heads, blocks of GLA_COLS value columns).  A column v of a head's state (its d values over the
+// key channels) is independent of the other columns: GLA_LANES lanes share it, lane l holding the key channels
+// l + GLA_LANES * i in registers, and a block of 128 threads runs 16 columns.  The tokens' q (scaled), k, decay and
+// v come into shared memory sixteen (the widest heads: eight) tokens at a time; every block forms the decays of its head itself
+// (alpha = exp(log_sigmoid(z + bias) / tau), float32).  Per token a lane does 2 NPER multiply-adds and the lanes'
+// parts of the output are summed by shuffles in a fixed order.
+// proj: rows [q: H*d | k: H*d | v: H*dv | ...] in T; z: [T, H*d] float32; state: [H][dv][d] floats per slot;
+// o: [T, H*dv] float32.
+constexpr int GLA_TOK_MAX = 16;
+constexpr int GLA_LANES = 8;
+constexpr int GLA_COLS = 128 / GLA_LANES;
+
+template <typename T, int NPER>
+__global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ z,
+                                                       const float* __restrict__ z_bias, int H, int d, int dv, float inv_tau,
+                                                       float q_scale, float* __restrict__ state, long long state_stride,
+                                                       const int* __restrict__ cu_q, const int* __restrict__ slots,
+                                                       float* __restrict__ o) {
+    constexpr int ROW = GLA_LANES * NPER;                           // a token's q (or k, or decay), zeros from d on
+    constexpr int GLA_TOK = NPER > 16 ? GLA_TOK_MAX / 2 : GLA_TOK_MAX;     // (static shared memory ends at 48 KB)
+    __shared__ float qs[GLA_TOK][ROW], ks[GLA_TOK][ROW], as[GLA_TOK][ROW], vs[GLA_TOK][GLA_COLS];
+    const int s = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * GLA_COLS;
+    const int slot = slots[s];
+    const int q0 = cu_q[s], nq = cu_q[s + 1] - q0;
+    if (slot < 0 || nq <= 0) return;
+    const int tid = threadIdx.x, lane = tid & (GLA_LANES - 1), col = tid / GLA_LANES;
+    const int v = v0 + col;
+    const bool ok = v < dv;
+    float* sp = state + (size_t)slot * state_stride + ((size_t)h * dv + (ok ? v : 0)) * d;
+    float S[NPER];
+#pragma unroll
+    for (int i = 0; i < NPER; ++i) S[i] = ok && lane + GLA_LANES * i < d ? sp[lane + GLA_LANES * i] : 0.f;
+    const T* q_src = proj + (size_t)h * d;
+    const T* k_src = proj + (size_t)H * d + (size_t)h * d;
+    const T* v_src = proj + (size_t)2 * H * d + (size_t)h * dv + v0;
+    const float* z_src = z + (size_t)h * d;
+    for (int t0 = 0; t0 < nq; t0 += GLA_TOK) {
+        const int nt = min(GLA_TOK, nq - t0);
+        for (int i = tid; i < GLA_TOK * ROW; i += 128) {
+            const int t = i / ROW, n = i - t * ROW;
+            float qv = 0.f, kv = 0.f, av = 1.f;
+            if (t < nt && n < d) {
+                const size_t row = (size_t)(q0 + t0 + t);
+                qv = to_float(q_src[row * ld + n]) * q_scale;
+                kv = to_float(k_src[row * ld + n]);
+                av = expf(log_sigmoid_f(z_src[row * (size_t)H * d + n] + __ldg(z_bias + h * d + n)) * inv_tau);
+            }
+            qs[t][n] = qv, ks[t][n] = kv, as[t][n] = av;
+        }
+        for (int i = tid; i < GLA_TOK * GLA_COLS; i += 128) {
+            const int t = i / GLA_COLS, c = i - t * GLA_COLS;
+            vs[t][c] = t < nt && v0 + c < dv ? to_float(v_src[(size_t)(q0 + t0 + t) * ld + c]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int t = 0; t < GLA_TOK; ++t) {
+            if (t < nt) {                                           // (uniform over the block)
+                const float vv = vs[t][col];
+                float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < NPER; ++i) {
+                    const int n = lane + GLA_LANES * i;
+                    S[i] = fmaf(as[t][n], S[i], ks[t][n] * vv);
+                    if (i & 1) acc1 = fmaf(S[i], qs[t][n], acc1); else acc0 = fmaf(S[i], qs[t][n], acc0);
+                }
+                float acc = acc0 + acc1;
+#pragma unroll
+                for (int m = GLA_LANES / 2; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+                if (ok && lane == 0) o[(size_t)(q0 + t0 + t) * H * dv + (size_t)h * dv + v] = acc;
+            }
+        }
+        __syncthreads();
+    }
+    if (ok) {
+#pragma unroll
+        for (int i = 0; i < NPER; ++i)
+            if (lane + GLA_LANES * i < d) sp[lane + GLA_LANES * i] = S[i];
+    }
+}
+
+PL_EXPORT int pl_gla_scan(const void* proj, int dtype, int ld, const float* z, const float* z_bias, int H, int d, int dv,
+                          float tau, float q_scale, float* state, long long state_stride, const int* cu_q, const int* slots,
+                          int num_seqs, float* o, cudaStream_t stream) {
+    if (num_seqs == 0) return 0;
+    PL_REQUIRE(H > 0 && d > 0 && d <= 256 && dv > 0 && tau > 0.f && ld >= 2 * H * d + H * dv,
+               "gla_scan: bad sizes H=%d d=%d dv=%d ld=%d (key size at most 256)", H, d, dv, ld);
+    const dim3 grid(num_seqs, H, (dv + GLA_COLS - 1) / GLA_COLS);
+    PL_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gla_scan: %d heads of %d values", H, dv);
+    const int nper = (d + GLA_LANES - 1) / GLA_LANES;
+#define PL_GLA(TT, N)                                                                                                     \
+    gla_scan_kernel<TT, N><<<grid, 128, 0, stream>>>((const TT*)proj, ld, z, z_bias, H, d, dv, 1.0f / tau, q_scale, state, \
+                                                     state_stride, cu_q, slots, o)
+#define PL_GLA_N(TT)                                                                                        \
+    do {                                                                                                    \
+        if (nper <= 2) PL_GLA(TT, 2); else if (nper <= 4) PL_GLA(TT, 4); else if (nper <= 8) PL_GLA(TT, 8); \
+        else if (nper <= 16) PL_GLA(TT, 16); else PL_GLA(TT, 32);                                           \
+    } while (0)
+    if (dtype == PL_F32) PL_GLA_N(float);
+    else if (dtype == PL_BF16) PL_GLA_N(__nv_bfloat16);
+    else return pl_fail("gla_scan: unknown dtype %d", dtype);
+#undef PL_GLA_N
+#undef PL_GLA
+    PL_LAUNCHED("gla_scan");
+    return 0;
+}
+
+// ------------------------------------------------------------------ norm per head, times silu(gate)
+// out[t, h*dv + c] = o[t, h, c] / sqrt(mean_c(o[t, h, :]^2) + eps) * w[c] * silu(gate[t, h*dv + c]); one warp per
+// (token, head); `gate`: columns of a row-major tensor with row stride ldg.
+template <typename T>
+__global__ void __launch_bounds__(256) head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ gate, int ldg,
+                                                             const float* __restrict__ w, float eps, T* __restrict__ out,
+                                                             long long rows, int H, int dv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long item = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (item >= rows * H) return;
+    const long long t = item / H;
+    const int h = (int)(item - t * H), lane = threadIdx.x & 31;
+    const float* orow = o + (size_t)item * dv;
+    float sq = 0.f;
+    for (int c = lane; c < dv; c += 32) {
+        const float x = orow[c];
+        sq = fmaf(x, x, sq);
+    }
+    sq = warp_sum(sq);
+    const float f = 1.0f / sqrtf(sq / (float)dv + eps);
+    const T* g = gate + (size_t)t * ldg + (size_t)h * dv;
+    T* dst = out + (size_t)item * dv;
+    for (int c = lane; c < dv; c += 32) dst[c] = from_float<T>(orow[c] * f * __ldg(w + c) * silu_f(to_float(g[c])));
+}
+
+PL_EXPORT int pl_head_norm_gate(const float* o, const void* gate, int dtype, int ldg, const float* w, float eps, void* out,
+                                long long rows, int H, int dv, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    PL_REQUIRE(rows > 0 && H > 0 && dv > 0, "head_norm_gate: bad sizes rows=%lld H=%d dv=%d", rows, H, dv);
+    const long long blocks = (rows * H + 7) / 8;
+    PL_REQUIRE(blocks < (1ll << 31), "head_norm_gate: %lld rows", rows);
+    if (dtype == PL_F32)
+        PL_CUDA(launch_pdl(head_norm_gate_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, o, (const float*)gate, ldg,
+                           w, eps, (float*)out, rows, H, dv));
+    else if (dtype == PL_BF16)
+        PL_CUDA(launch_pdl(head_norm_gate_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, o,
+                           (const __nv_bfloat16*)gate, ldg, w, eps, (__nv_bfloat16*)out, rows, H, dv));
+    else
+        return pl_fail("head_norm_gate: unknown dtype %d", dtype);
+    return 0;
+}

@@ -213,9 +213,17 @@ class CudaOps:
         return out
 
     # ---- embedding, norms, activation ------------------------------------------
-    def embedding(self, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
-        """Rows of `table` as the float32 stream, each element times `scale`."""
+    def embedding(self, table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0, copies: int = 1) -> torch.Tensor:
+        """Rows of `table` as the float32 stream, each element times `scale`; with `copies` > 1 every row is laid
+        out that many times side by side (a model of several residual streams)."""
         T, (V, H) = ids.numel(), table.shape
+        if copies > 1:
+            lib = load_module("streams")
+            out = torch.empty((T, H * copies), dtype=torch.float32, device=self.device)
+            _check(lib, lib.pl_embedding_copies(self._p(table), self._code(table), self._p(ids), self._p(out), T, H, V,
+                                                c_float(scale), copies, self._stream))
+            self.launches += 1
+            return out
         out = torch.empty((T, H), dtype=torch.float32, device=self.device)
         _check(self.core, self.core.pl_embedding(self._p(table), self._code(table), self._p(ids), self._p(out),
                                                  T, H, V, c_float(scale), self._stream))
@@ -439,7 +447,8 @@ class CudaOps:
         return qkv
 
     # ---- mixers that are not plain grouped-query attention ----------------------------
-    def heads_linear(self, x: torch.Tensor, col0: int, head_stride: int, w: torch.Tensor) -> torch.Tensor:
+    def heads_linear(self, x: torch.Tensor, col0: int, head_stride: int, w: torch.Tensor,
+                     out_float32: bool = False) -> torch.Tensor:
         """A product per head: out[t, h, :] = w[h] @ x[t, col0 + h * head_stride : ... + K] for w [heads, N, K];
         returns [T, heads * N].  float32: this package's CUDA-core product, head by head on strided operands;
         bfloat16: the library's batched product."""
@@ -456,6 +465,8 @@ class CudaOps:
                 self.launches += 1
             return out
         xv = torch.as_strided(x, (nh, T, K), (head_stride, ld, 1), x.storage_offset() + col0)
+        if out_float32:
+            return torch.bmm(xv, w.transpose(1, 2), out_dtype=torch.float32).transpose(0, 1).reshape(T, nh * N)
         return torch.bmm(xv, w.transpose(1, 2)).transpose(0, 1).reshape(T, nh * N)
 
     def normed_qkv_write(self, proj, nh, nkv, d, dv, D, q_weight, k_weight, eps, ctx, kv, block_table, has_kv=True,
@@ -552,6 +563,173 @@ class CudaOps:
         _check(lib, lib.pl_gated_group_norm(self._p(y), self._p(zx), self._code(zx), ld, self._p(norm_w), c_float(eps),
                                             self._p(out), T, inner, norm_groups, self._p(ctx.token_seq), self._stream))
         self.launches += 3
+        return out
+
+    # ---- several residual streams, norms in parts, PolyNorm ---------------------------
+    def stream_norm(self, x, streams, branch, mix, out, w_in, norm_w, groups, eps, branch2=None, scales=None, biases=None):
+        """One kernel at a sublayer boundary of a model with `streams` copies of the residual stream
+        (x: [rows, streams * W] float32, updated in place): the copies take `branch` [rows, W] in
+        (x_t <- sum_s mix[s, t] x_s + out[t] * branch with `mix` [S, S] and `out` [S]; without `mix` every copy gets
+        + branch), the next input u = sum_s w_in[s] x_s (w_in None: the plain sum) is formed and normed in `groups`
+        equal consecutive parts, each divided by its own root mean square, times `norm_w`.  With `branch2` the branch
+        is scales[0] * (branch + biases[0]) + scales[1] * (branch2 + biases[1]) (biases float32 [W] or None)."""
+        lib = load_module("streams")
+        rows, SW = x.shape
+        W = SW // streams
+        assert x.dtype == torch.float32 and x.is_contiguous() and W * streams == SW
+        for t in (mix, out, w_in):
+            assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+        if branch is not None:
+            assert branch.shape == (rows, W) and branch.is_contiguous()
+        if branch2 is not None:
+            assert branch2.shape == (rows, W) and branch2.is_contiguous() and branch2.dtype == branch.dtype
+        sa, sb = scales if scales is not None else (1.0, 1.0)
+        ba, bb = biases if biases is not None else (None, None)
+        y = torch.empty((rows, W), dtype=self.compute_dtype, device=self.device)
+        _check(lib, lib.pl_stream_norm(self._p(x), self._p(branch), self._p(branch2),
+                                       self._code(branch) if branch is not None else PL_F32, self._p(ba), self._p(bb),
+                                       c_float(sa), c_float(sb), self._p(mix), self._p(out), self._p(w_in), self._p(norm_w),
+                                       self._code(norm_w), self._p(y), self._code(y), c_longlong(rows), streams, W, groups,
+                                       c_float(eps), self._stream))
+        self.launches += 1
+        return y
+
+    def poly_norm(self, z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
+        """coef[0] N(z) + coef[1] N(z^2) + coef[2] N(z^3) + coef[3] row by row, N(v) = v / sqrt(mean(v^2) + eps)."""
+        lib = load_module("streams")
+        rows, F = z.shape
+        assert z.is_contiguous() and coef.dtype == torch.float32 and coef.numel() == 4
+        out = torch.empty_like(z)
+        _check(lib, lib.pl_poly_norm(self._p(z), self._code(z), self._p(coef), c_float(eps), self._p(out), c_longlong(rows), F,
+                                     self._stream))
+        self.launches += 1
+        return out
+
+    def add_bias(self, y: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+        """y[r, :] += bias in place (bias float32)."""
+        lib = load_module("streams")
+        rows, W = y.shape
+        assert y.is_contiguous() and bias.dtype == torch.float32 and bias.numel() == W
+        _check(lib, lib.pl_add_bias(self._p(y), self._code(y), self._p(bias), c_longlong(rows), W, self._stream))
+        self.launches += 1
+        return y
+
+    def scaled_sum(self, a, scale_a, bias_a, b, scale_b, bias_b) -> torch.Tensor:
+        """scale_a * (a + bias_a) + scale_b * (b + bias_b) as float32 (either bias may be None)."""
+        lib = load_module("streams")
+        rows, W = a.shape
+        assert a.is_contiguous() and b.is_contiguous() and a.shape == b.shape and a.dtype == b.dtype
+        out = torch.empty((rows, W), dtype=torch.float32, device=self.device)
+        _check(lib, lib.pl_scaled_sum(self._p(a), self._p(b), self._code(a), self._p(bias_a), self._p(bias_b), c_float(scale_a),
+                                      c_float(scale_b), self._p(out), c_longlong(rows), W, self._stream))
+        self.launches += 1
+        return out
+
+    # ---- attention whose values are rotated too ---------------------------------------
+    @staticmethod
+    def _rot_args(position):
+        if position is None:
+            return c_void_p(0), 0, 0, 0
+        t = position.table
+        return c_void_p(t.data_ptr()), t.shape[0], position.rotary_dim, 1 if position.pairing == "interleaved" else 0
+
+    def rotated_qkv_write(self, proj, bias, nh, nkv, d, dv, D, position, value_position, ctx, kv, block_table,
+                          write=True) -> torch.Tensor:
+        """proj rows [q: nh*d | k: nkv*d | v: nkv*dv | ...] (+ `bias`, float32, the same layout): q and k are rotated
+        by the token's position with `position`, v with `value_position`; returns the queries [T, nh*D] (heads padded
+        to D with zeros) and writes keys and values, padded the same way, to their page slots."""
+        T, ld = proj.shape
+        assert proj.is_contiguous() and kv.is_contiguous() and kv.dtype == proj.dtype and kv.shape[4] == D
+        assert bias is None or (bias.dtype == torch.float32 and bias.numel() == nh * d + nkv * (d + dv))
+        q = torch.empty((T, nh * D), dtype=proj.dtype, device=self.device)
+        _check(self.core, self.core.pl_rotated_qkv_write(
+            self._p(proj), self._code(proj), T, ld, self._p(bias), self._p(q), self._p(kv), self._p(ctx.positions),
+            self._p(ctx.token_seq), self._p(block_table), block_table.shape[1], kv.shape[0], kv.shape[3],
+            *self._rot_args(position), *self._rot_args(value_position), nh, nkv, d, dv, D, 1 if write else 0, self._stream))
+        self.launches += 1
+        return q
+
+    def head_unrotate_gate(self, o, nh, D, dv, value_position, ctx, gate=None) -> torch.Tensor:
+        """[T, nh*dv]: the first dv columns of each head of o [T, nh*D], turned back by the query's position with
+        `value_position`, times sigmoid(gate[t, h]) if a gate (a column view [T, nh] of a row-major tensor) is given."""
+        T = o.shape[0]
+        assert o.is_contiguous() and o.shape[1] == nh * D
+        out = torch.empty((T, nh * dv), dtype=o.dtype, device=self.device)
+        ldg = 0
+        if gate is not None:
+            assert gate.dtype == o.dtype and gate.stride(1) == 1 and gate.shape == (T, nh)
+            ldg = gate.stride(0)
+        _check(self.core, self.core.pl_head_unrotate_gate(self._p(o), self._code(o), T, D, self._p(gate), ldg,
+                                                          self._p(ctx.positions), self._p(ctx.token_seq),
+                                                          *self._rot_args(value_position), self._p(out), nh, dv,
+                                                          self._stream))
+        self.launches += 1
+        return out
+
+    # ---- mixers with a state of fixed size: convolution + gated recurrence, gated linear attention --------------
+    def causal_conv(self, yx, col0, C, b_in, conv_w, conv_b, state, ctx):
+        """u = conv(yx[:, col0:col0+C] + b_in[col0:col0+C]) + conv_b per channel, causal, `taps` wide; the request's
+        last taps-1 inputs are the first (taps-1)*C floats of its state slot and are replaced by the new ones.
+        Returns (u float32 [T, C], u in the compute dtype)."""
+        lib = load_module("recurrent")
+        T, ld = yx.shape
+        taps = conv_w.shape[1]
+        assert yx.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2
+        assert conv_w.dtype == torch.float32 and conv_w.shape == (C, taps) and conv_w.is_contiguous()
+        u = torch.empty((T, C), dtype=torch.float32, device=self.device)
+        low = u if yx.dtype == torch.float32 else torch.empty((T, C), dtype=yx.dtype, device=self.device)
+        _check(lib, lib.pl_causal_conv(self._p(yx), self._code(yx), ld, col0, C, self._p(b_in), self._p(conv_w),
+                                       self._p(conv_b), taps, self._p(state), c_longlong(state.shape[1]),
+                                       self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), ctx.num_seqs, max(T, 1),
+                                       self._p(u), self._p(low) if low is not u else c_void_p(0), self._stream))
+        self.launches += 1
+        return u, low
+
+    def gated_recurrence(self, gates, b_gates, u, yx, b_in, rate, blocks, taps, state, ctx) -> torch.Tensor:
+        """S_t = a S_(t-1) + sqrt(1 - a^2) sigmoid(g_i) u_t with a = exp(rate * sigmoid(g_r)); returns
+        S_t * gelu_tanh(yx[:, :C] + b_in[:C]) in the compute dtype.  gates: float32 [T, blocks * 2 * bw], per block
+        [recurrence gate | input gate]; S lives behind the convolution's inputs in the state slot."""
+        lib = load_module("recurrent")
+        T, C = u.shape
+        ld = yx.shape[1]
+        assert gates.dtype == torch.float32 and gates.is_contiguous() and gates.shape == (T, 2 * C)
+        assert u.dtype == torch.float32 and u.is_contiguous() and yx.is_contiguous() and state.shape[1] == taps * C
+        out = torch.empty((T, C), dtype=yx.dtype, device=self.device)
+        _check(lib, lib.pl_gated_recurrence(self._p(gates), self._p(b_gates), self._p(u), self._p(yx), self._code(yx), ld,
+                                            self._p(b_in), self._p(rate), C, blocks, self._p(state),
+                                            c_longlong(state.shape[1]), c_longlong((taps - 1) * C),
+                                            self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), ctx.num_seqs,
+                                            max(int(ctx.max_q_len), 1),
+                                            self._p(out), self._stream))
+        self.launches += 1
+        return out
+
+    def linear_attention_scan(self, proj, z, z_bias, H, d, dv, tau, q_scale, state, ctx) -> torch.Tensor:
+        """Gated linear attention's recurrence.  proj rows [q: H*d | k: H*d | v: H*dv | ...]; z float32 [T, H*d] the
+        decay's pre-activation (bias `z_bias`): alpha = sigmoid(z)^(1/tau); S_t = diag(alpha_t) S_(t-1) + k_t v_t^T,
+        o_t = S_t^T (q_t * q_scale).  state: [slots, H*dv*d] float32, updated in place.  Returns o float32 [T, H*dv]."""
+        lib = load_module("recurrent")
+        T, ld = proj.shape
+        assert proj.is_contiguous() and z.dtype == torch.float32 and z.is_contiguous() and z.shape == (T, H * d)
+        assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == H * dv * d
+        o = torch.empty((T, H * dv), dtype=torch.float32, device=self.device)
+        _check(lib, lib.pl_gla_scan(self._p(proj), self._code(proj), ld, self._p(z), self._p(z_bias), H, d, dv, c_float(tau),
+                                    c_float(q_scale), self._p(state), c_longlong(state.shape[1]), self._p(ctx.cu_seqlens_q),
+                                    self._p(ctx.state_slots), ctx.num_seqs, self._p(o), self._stream))
+        self.launches += 1
+        return o
+
+    def head_norm_gate(self, o, proj, g_col0, H, dv, norm_w, eps) -> torch.Tensor:
+        """Each head of o (float32 [T, H*dv]) divided by its root mean square over dv, times `norm_w` [dv], times
+        silu(proj[:, g_col0 : g_col0 + H*dv]); in the compute dtype."""
+        lib = load_module("recurrent")
+        T = o.shape[0]
+        assert o.is_contiguous() and proj.is_contiguous() and norm_w.dtype == torch.float32 and norm_w.numel() == dv
+        out = torch.empty((T, H * dv), dtype=proj.dtype, device=self.device)
+        gate = c_void_p(proj.data_ptr() + g_col0 * proj.element_size())
+        _check(lib, lib.pl_head_norm_gate(self._p(o), gate, self._code(proj), proj.shape[1], self._p(norm_w), c_float(eps),
+                                          self._p(out), c_longlong(T), H, dv, self._stream))
+        self.launches += 1
         return out
 
     # ---- routed experts ----------------------------------------------------------
