@@ -127,9 +127,10 @@ __global__ void __launch_bounds__(256) gated_recurrence_kernel(const float* __re
             if (ok && ta + i < nq) {
                 const size_t row = (size_t)(q0 + ta + i);
                 const float r = sigmoid_f(gates[row * G + gr] + br), in = sigmoid_f(gates[row * G + gi] + bi);
-                const float av = expf(rt * r);
-                a[i] = av;
-                b[i] = sqrtf(fmaxf(1.0f - av * av, 0.f)) * in * u[row * C + c];
+                // 1 - a^2 = -expm1(2 log a): formed from the exponent, so that nothing cancels where a is close to 1
+                const float la = rt * r;
+                a[i] = expf(la);
+                b[i] = sqrtf(fmaxf(-expm1f(2.0f * la), 0.f)) * in * u[row * C + c];
             }
             A *= a[i];
             B = fmaf(a[i], B, b[i]);

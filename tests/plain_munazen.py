@@ -7,11 +7,23 @@ dictionary of tensors by checkpoint name, and keeps no cache: every function see
 
 from __future__ import annotations
 
+import contextlib
 import math
 
 import torch
 
 F = torch.float64
+
+
+@contextlib.contextmanager
+def precision(dtype):
+    """Runs the plain model in another precision (float32: what rounding alone does to a given model)."""
+    global F
+    old, F = F, dtype
+    try:
+        yield
+    finally:
+        F = old
 
 
 def group_rms(x, weight, groups, eps):
