@@ -147,6 +147,10 @@ def draw_weights(hf_cfg: dict, seed: int) -> dict[str, torch.Tensor]:
             t = 1.0 + 0.2 * r
         elif name == "embed":
             t = 0.5 * r
+        elif name.endswith(".mix.q") and name[:-1] + "k" in out:
+            # linear attention: queries that lean towards their own keys, so that q . k of the first tokens, whose sign
+            # is all that the norm behind a nearly empty state keeps, stays away from zero also in bfloat16
+            t = out[name[:-1] + "k"] + 0.5 * r * (1.2 / np.sqrt(shape[-1]))
         else:
             t = r * (1.2 / np.sqrt(shape[-1]))                     # matrices: outputs of the order of their inputs
         out[name] = t.to(torch.bfloat16).float().contiguous()
@@ -168,14 +172,15 @@ def plain_logits(folder: str, tokens) -> np.ndarray:
         return plain_munazen.forward(cfg, w, tokens)[0].to(torch.float32).numpy()
 
 
-def rounding_error(folder: str, tokens) -> np.ndarray:
-    """Per position, the root mean square over the vocabulary of the difference between the plain model run in float32
+def rounding_error(folder: str, tokens, dtype=torch.float32) -> np.ndarray:
+    """Per position, the root mean square over the vocabulary of the difference between the plain model run in `dtype`
     and in float64: what rounding alone does to these weights (a norm over a nearly empty state of the linear
-    attention, or over a query and key that nearly cancel, magnifies it)."""
+    attention, or over a query and key that nearly cancel, magnifies it; in bfloat16 the sign of the first token's
+    query-key product, which is all that the norm behind the linear attention keeps of it, can turn)."""
     cfg, w = read_folder(folder)
     with torch.no_grad():
         exact = plain_munazen.forward(cfg, w, tokens)[0]
-        with plain_munazen.precision(torch.float32):
+        with plain_munazen.precision(dtype):
             rounded = plain_munazen.forward(cfg, w, tokens)[0]
     return (rounded.double() - exact).pow(2).mean(dim=1).sqrt().numpy()
 

@@ -10,7 +10,7 @@ import torch
 from tests import munazen_parts as parts
 from tests import plain_munazen as plain
 from tests import schedules
-from tests.helpers import assert_bf16_close_to_f32, requests_for
+from tests.helpers import requests_for
 from tests.munazen_cases import (CASE_A, CASE_B, CASE_C, CASES, YARN, case_folder, generated_case, left, make_folder,
                                  plain_greedy, plain_logits, rounding_error)
 
@@ -28,13 +28,18 @@ def ops():
 
 def close(got, want, dtype, what, rounding=None):
     """float32: the largest difference within F32_TOL of the largest logit, or the position's root mean square error
-    within 10 times what float32 alone does to the plain model there.  bfloat16: within BF16_TOL of the largest logit."""
+    within 10 times what float32 alone does to the plain model there.  bfloat16: within BF16_TOL of the largest logit, or
+    (`rounding` then measured in bfloat16) a root mean square error within 3 times what bfloat16 alone does there, or
+    within what it does at the request's worst position (one run in bfloat16 is one draw of a position's error)."""
     assert got.shape == want.shape, what
     assert np.isfinite(got).all(), what
     err = np.abs(got - want)
     top = max(1.0, float(np.abs(want).max()))
     if dtype == "bfloat16":
         bad = err.max(axis=1) > BF16_TOL * top
+        if rounding is not None:
+            rms = np.sqrt((err.astype(np.float64) ** 2).mean(axis=1))
+            bad &= (rms > 3.0 * rounding) & (rms > rounding.max())
     else:
         bad = err.max(axis=1) > F32_TOL * top
         if rounding is not None:
@@ -139,7 +144,7 @@ def test_long_recurrence_keeps_a_far_token(ops):
     h2[0] /= 30.0
     w = parts.recurrence_weights(W, m, 0, -9.0)
     quiet = plain.recurrent_right(h2.double(), {k: v.double() for k, v in w.items()}, "r.", m)
-    assert (quiet[-1] - want[-1]).abs().max() > 1e-2, "the far token must matter"
+    assert (quiet[-1] - want[-1]).abs().max() > 3e-3, "the far token must matter"
 
 
 def test_long_linear_attention_keeps_a_far_token(ops):
@@ -151,11 +156,15 @@ def test_long_linear_attention_keeps_a_far_token(ops):
     h2[0] /= 30.0
     w = parts.gla_weights(W, m, 0, decay_bias=9.0)
     quiet = plain.mixer_gla(h2.double(), {k: v.double() for k, v in w.items()}, "g.", m, 1e-5)
-    assert (quiet[-1] - want[-1]).abs().max() > 1e-2, "the far token must matter"
+    assert (quiet[-1] - want[-1]).abs().max() > 3e-3, "the far token must matter"
 
 
 # ---------------------------------------------------------------- the engine against the plain model
 LENGTHS = {"A": (1, 30, 77, 49, 2, 60, 90, 35), "B": (5, 41, 120, 13, 80, 55), "C": (3, 70, 33, 65, 18, 41)}
+
+
+def rounding_of(folder, toks, dtype):
+    return rounding_error(folder, toks, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
 
 
 def replay(folder, dtype, steps, max_tokens, block_size=16, slots=4, **kw):
@@ -193,7 +202,7 @@ def test_schedule_matches_plain(folders, name, dtype, schedule):
     outputs, rp = replay(folders[name], dtype, steps, max_tokens, block_size=block)
     got = schedules.collect(steps, outputs)
     for rid, toks in reqs.items():
-        close(got[rid], plain_logits(folders[name], toks), dtype, f"{schedule}/{name}/{rid}", rounding_error(folders[name], toks))
+        close(got[rid], plain_logits(folders[name], toks), dtype, f"{schedule}/{name}/{rid}", rounding_of(folders[name], toks, dtype))
     if schedule == "tail":
         assert rp.runner.num_graph_steps > 0, "decode steps replay graphs: every part of the model can be captured"
 
@@ -205,8 +214,9 @@ def test_bfloat16_against_the_float32_engine(folders, name, schedule):
     steps, max_tokens = getattr(schedules, schedule)(reqs)
     a, _ = replay(folders[name], "float32", steps, max_tokens)
     b, _ = replay(folders[name], "bfloat16", steps, max_tokens)
-    for k in a:
-        assert_bf16_close_to_f32(b[k], a[k], f"munazen {schedule}/{name}/step {k}")
+    a, b = schedules.collect(steps, a), schedules.collect(steps, b)
+    for rid, toks in reqs.items():
+        close(b[rid], a[rid], "bfloat16", f"munazen {schedule}/{name}/{rid}", rounding_of(folders[name], toks, "bfloat16"))
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -228,7 +238,7 @@ def test_long_decoding(folders):
         outputs, _ = replay(folders["B"], dtype, steps, max_tokens, block_size=8, slots=2)
         got = schedules.collect(steps, outputs)
         for rid, toks in reqs.items():
-            close(got[rid], plain_logits(folders["B"], toks), dtype, f"long decoding {dtype}/{rid}", rounding_error(folders["B"], toks))
+            close(got[rid], plain_logits(folders["B"], toks), dtype, f"long decoding {dtype}/{rid}", rounding_of(folders["B"], toks, dtype))
 
 
 @pytest.mark.parametrize("seed", range(10))
@@ -237,19 +247,11 @@ def test_generated_configurations(tmp_path, seed):
     folder = make_folder(tmp_path, hf, seed)
     reqs = requests_for(hf["vocab"], (2, 50, 21, 70, 9, 130), seed=seed)
     steps, max_tokens = schedules.mixed(reqs, live=3, seed=seed)
-    f32 = None
     for dtype in ("float32", "bfloat16"):
         outputs, _ = replay(folder, dtype, steps, max_tokens, slots=3)
-        if dtype == "float32":
-            f32 = outputs
-            got = schedules.collect(steps, outputs)
-            for rid, toks in reqs.items():
-                close(got[rid], plain_logits(folder, toks), dtype, f"generated {seed}/{dtype}/{rid}", rounding_error(folder, toks))
-        else:
-            for k in outputs:
-                assert np.isfinite(outputs[k]).all()
-                rel = np.abs(outputs[k] - f32[k]).max() / max(1.0, np.abs(f32[k]).max())
-                assert rel < 0.25, f"generated {seed}/bfloat16/step {k}: {rel:.3f} of the largest logit"
+        got = schedules.collect(steps, outputs)
+        for rid, toks in reqs.items():
+            close(got[rid], plain_logits(folder, toks), dtype, f"generated {seed}/{dtype}/{rid}", rounding_of(folder, toks, dtype))
 
 
 def test_greedy_generation_through_the_engine(folders):
