@@ -85,6 +85,17 @@ ROKARAX_SIZES = {
     "r-tiny": dict(vocab=256, width=128, heads=4, kv_heads=2, dim=32, ff=256, window=64, q_rank=48, kv_rank=32,
                    rot_dim=16, ssm_heads=8, ssm_dim=16, state=16, groups=2, conv=3),
 }
+# Munazen at the layer sizes of a 2k- and a 4k-wide model: attention beside a gated recurrence of the model's width, and
+# gated linear attention with keys half and values once the model's width
+MUNAZEN_SIZES = {
+    "m-2k": dict(vocab=32000, width=2048, heads=16, kv_heads=4, dim=128, ff=8192, rec_width=2048, rec_blocks=16, conv=4,
+                 gla_heads=8, gla_dim=128, gla_vdim=256, streams=2, norm_groups=2),
+    "m-4k": dict(vocab=32000, width=4096, heads=32, kv_heads=8, dim=128, ff=14336, rec_width=4096, rec_blocks=16, conv=4,
+                 gla_heads=16, gla_dim=128, gla_vdim=256, streams=4, norm_groups=4),
+    # for trying the option out quickly; never a result
+    "m-tiny": dict(vocab=256, width=128, heads=4, kv_heads=2, dim=32, ff=256, rec_width=96, rec_blocks=3, conv=3,
+                   gla_heads=2, gla_dim=16, gla_vdim=32, streams=2, norm_groups=2),
+}
 PROMPT_LEN, DECODE_LEN, PREFILL_TOKENS, BLOCK_SIZE = 512, 256, 2048, 16
 RAGGED_PROMPTS, RAGGED_OUTPUTS = (128, 4096), (64, 512)      # the ragged serving workload: lengths drawn uniformly
 
@@ -624,6 +635,26 @@ def rokarax_configs(name: str):
     return rok, llama, len(order)
 
 
+def munazen_configs(name: str):
+    """(Munazen configuration dict, Llama configuration dict of equal size, number of layers)."""
+    s = MUNAZEN_SIZES[name]
+    left = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5,
+            "rot": {"dims": s["dim"], "base": 500000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    par = {"left": left, "right": {"width": s["rec_width"], "blocks": s["rec_blocks"], "conv": s["conv"]},
+           "left_scale": 1.0, "right_scale": 1.0}
+    gla = {"heads": s["gla_heads"], "dim": s["gla_dim"], "vdim": s["gla_vdim"], "tau": 16.0}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    order = [("parallel", par), ("gla", gla), ("parallel", par), ("parallel", par), ("gla", gla), ("parallel", par)]
+    mun = {"architecture": "Munazen", "vocab": s["vocab"], "width": s["width"], "streams": s["streams"],
+           "norm": {"eps": 1e-6, "groups": s["norm_groups"]},
+           "layers": [{"type": t, "mixer": m, "mlp": dense} for t, m in order]}
+    llama = {"architectures": ["LlamaForCausalLM"], "vocab_size": s["vocab"], "hidden_size": s["width"],
+             "intermediate_size": s["ff"], "num_hidden_layers": len(order), "num_attention_heads": s["heads"],
+             "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"], "rope_theta": 500000.0, "rms_norm_eps": 1e-6,
+             "tie_word_embeddings": False, "max_position_embeddings": 8192}
+    return mun, llama, len(order)
+
+
 def compare_with_llama(args, label: str, size: str, sizes: dict, model: dict, llama: dict, runs: int) -> dict:
     """Prefill and decode of another decoder at layer sizes of a real model (random weights drawn on the
     device) beside a Llama of equal width, heads and layer runs: device-timed with CUDA events, with the device
@@ -678,6 +709,11 @@ def rokarax_compare(args) -> dict:
     return compare_with_llama(args, "rokarax", args.rokarax_size, ROKARAX_SIZES[args.rokarax_size], rok, llama, runs)
 
 
+def munazen_compare(args) -> dict:
+    mun, llama, runs = munazen_configs(args.munazen_size)
+    return compare_with_llama(args, "munazen", args.munazen_size, MUNAZEN_SIZES[args.munazen_size], mun, llama, runs)
+
+
 def run_ours(args) -> dict:
     import torch
     from paged_llm_b200 import EngineConfig, LLMEngine
@@ -687,6 +723,8 @@ def run_ours(args) -> dict:
         return pomisun_compare(args)
     if args.only == "rokarax":
         return rokarax_compare(args)
+    if args.only == "munazen":
+        return munazen_compare(args)
     if args.only == "validate":
         return validate(args)
     if args.only == "sample":
@@ -883,12 +921,14 @@ def main() -> int:
                     help="with --only pomisun: the layer sizes (the Llama beside it gets the same)")
     ap.add_argument("--rokarax-size", choices=sorted(ROKARAX_SIZES), default="r-2k",
                     help="with --only rokarax: the layer sizes (the Llama beside it gets the same)")
-    ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate", "sample", "pomisun", "rokarax"], default=None,
+    ap.add_argument("--munazen-size", choices=sorted(MUNAZEN_SIZES), default="m-2k",
+                    help="with --only munazen: the layer sizes (the Llama beside it gets the same)")
+    ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate", "sample", "pomisun", "rokarax", "munazen"], default=None,
                     help="run only the decode loop, only the prefill step, the ragged serving workload through "
                          "LLMEngine.generate, one mixed step (--batch decoding requests of --context tokens beside one "
                          "portion of --prefill-tokens), the float32 validation run, the sampler's kernels on --batch rows, or "
-                         "prefill and decode of the Pomisun or the Rokarax decoder beside a Llama of equal size (--pomisun-size, "
-                         "--rokarax-size), and print "
+                         "prefill and decode of the Pomisun, the Rokarax or the Munazen decoder beside a Llama of equal size "
+                         "(--pomisun-size, --rokarax-size, --munazen-size), and print "
                          "a short line")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:

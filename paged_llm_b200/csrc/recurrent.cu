@@ -95,7 +95,25 @@ PL_EXPORT int pl_causal_conv(const void* in, int dtype, int ld, int col0, int C,
 // same; channel c belongs to block c / bw.  The state S of a request: `state_off` floats into its slot.
 constexpr int REC_SEG = 8;
 
-template <typename T, int TL>
+// The decays and drives of all tokens at once, in place: gates[t, r-part of c] <- a, gates[t, i-part of c] <- b.  A long
+// prompt's transcendental work is spread over the whole device here, and the scan behind it only multiplies and adds.
+__global__ void __launch_bounds__(256) recurrence_prepare_kernel(float* __restrict__ gates, const float* __restrict__ b_gates,
+                                                                 const float* __restrict__ u, const float* __restrict__ rate,
+                                                                 int C, int bw, long long n) {
+    const int G = (C / bw) * 2 * bw;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long row = i / C;
+        const int c = (int)(i - row * C);
+        const int blk = c / bw, j = c - blk * bw;
+        const int gr = blk * 2 * bw + j, gi = gr + bw;
+        const float r = sigmoid_f(gates[row * G + gr] + __ldg(b_gates + gr)), in = sigmoid_f(gates[row * G + gi] + __ldg(b_gates + gi));
+        const float la = __ldg(rate + c) * r;
+        gates[row * G + gr] = expf(la);
+        gates[row * G + gi] = sqrtf(fmaxf(-expm1f(2.0f * la), 0.f)) * in * u[i];
+    }
+}
+
+template <typename T, int TL, bool PRE>
 __global__ void __launch_bounds__(256) gated_recurrence_kernel(const float* __restrict__ gates, const float* __restrict__ b_gates,
                                                                const float* __restrict__ u, const T* __restrict__ yx, int ld,
                                                                const float* __restrict__ b_y, const float* __restrict__ rate,
@@ -124,7 +142,12 @@ __global__ void __launch_bounds__(256) gated_recurrence_kernel(const float* __re
 #pragma unroll
         for (int i = 0; i < REC_SEG; ++i) {
             a[i] = 1.f, b[i] = 0.f;
-            if (ok && ta + i < nq) {
+            if (PRE) {
+                if (ok && ta + i < nq) {
+                    const size_t row = (size_t)(q0 + ta + i);
+                    a[i] = gates[row * G + gr], b[i] = gates[row * G + gi];
+                }
+            } else if (ok && ta + i < nq) {
                 const size_t row = (size_t)(q0 + ta + i);
                 const float r = sigmoid_f(gates[row * G + gr] + br), in = sigmoid_f(gates[row * G + gi] + bi);
                 // 1 - a^2 = -expm1(2 log a): formed from the exponent, so that nothing cancels where a is close to 1
@@ -162,25 +185,34 @@ __global__ void __launch_bounds__(256) gated_recurrence_kernel(const float* __re
     if (ok && lane_t == 0) *sp = S0;
 }
 
-// yx: the projection's rows [y: C | ...] with row stride ld in `dtype`; out: [T, C] in `dtype`.
-PL_EXPORT int pl_gated_recurrence(const float* gates, const float* b_gates, const float* u, const void* yx, int dtype, int ld,
+// yx: the projection's rows [y: C | ...] with row stride ld in `dtype`; out: [T, C] in `dtype`.  With more than a few tokens
+// in a request the gates [total_tokens, 2C] are overwritten by the decays and drives (recurrence_prepare_kernel).
+PL_EXPORT int pl_gated_recurrence(float* gates, const float* b_gates, const float* u, const void* yx, int dtype, int ld,
                                   const float* b_y, const float* rate, int C, int blocks, float* state,
                                   long long state_stride, long long state_off, const int* cu_q, const int* slots,
-                                  int num_seqs, int max_tokens, void* out, cudaStream_t stream) {
+                                  int num_seqs, int max_tokens, long long total_tokens, void* out, cudaStream_t stream) {
     if (num_seqs == 0) return 0;
     PL_REQUIRE(C > 0 && blocks > 0 && C % blocks == 0 && ld >= C, "gated_recurrence: bad sizes C=%d blocks=%d ld=%d", C, blocks, ld);
     const int bw = C / blocks;
     const bool few = max_tokens <= 2 * REC_SEG;
-    const int CH = few ? 256 : 32;
+    const bool many = max_tokens > 32 * REC_SEG;                     // long prompts: more token lanes, more blocks
+    const int CH = few ? 256 : many ? 8 : 32;
     const dim3 grid(num_seqs, (C + CH - 1) / CH);
     PL_REQUIRE(grid.y <= 65535, "gated_recurrence: %d channels", C);
 #define PL_REC(TT, L)                                                                                                      \
-    gated_recurrence_kernel<TT, L><<<grid, 256, 0, stream>>>(gates, b_gates, u, (const TT*)yx, ld, b_y, rate, C, bw, state, \
-                                                             state_stride, state_off, cu_q, slots, (TT*)out)
+    gated_recurrence_kernel<TT, L, L != 1><<<grid, 256, 0, stream>>>(gates, b_gates, u, (const TT*)yx, ld, b_y, rate, C, bw,   \
+                                                                     state, state_stride, state_off, cu_q, slots, (TT*)out)
+    if (!few) {
+        PL_REQUIRE(total_tokens > 0, "gated_recurrence: %lld tokens", total_tokens);
+        const long long n = total_tokens * C, blocks = (n + 255) / 256;
+        recurrence_prepare_kernel<<<(unsigned)(blocks < 65535 * 16 ? blocks : 65535 * 16), 256, 0, stream>>>(gates, b_gates, u, rate,
+                                                                                                          C, bw, n);
+        PL_LAUNCHED("recurrence_prepare");
+    }
     if (dtype == PL_F32) {
-        if (few) PL_REC(float, 1); else PL_REC(float, 8);
+        if (few) PL_REC(float, 1); else if (!many) PL_REC(float, 8); else PL_REC(float, 32);
     } else if (dtype == PL_BF16) {
-        if (few) PL_REC(__nv_bfloat16, 1); else PL_REC(__nv_bfloat16, 8);
+        if (few) PL_REC(__nv_bfloat16, 1); else if (!many) PL_REC(__nv_bfloat16, 8); else PL_REC(__nv_bfloat16, 32);
     } else {
         return pl_fail("gated_recurrence: unknown dtype %d", dtype);
     }
@@ -190,44 +222,90 @@ PL_EXPORT int pl_gated_recurrence(const float* gates, const float* b_gates, cons
 }
 
 // ------------------------------------------------------------------ gated linear attention, the recurrence
-// grid: (requests, heads, blocks of GLA_COLS value columns).  A column v of a head's state (its d values over the
-// key channels) is independent of the other columns: GLA_LANES lanes share it, lane l holding the key channels
-// l + GLA_LANES * i in registers, and a block of 128 threads runs 16 columns.  The tokens' q (scaled), k, decay and
-// v come into shared memory sixteen (the widest heads: eight) tokens at a time; every block forms the decays of its head itself
-// (alpha = exp(log_sigmoid(z + bias) / tau), float32).  Per token a lane does 2 NPER multiply-adds and the lanes'
-// parts of the output are summed by shuffles in a fixed order.
+// A column v of a head's state (its d values over the key channels) is independent of the other columns: GLA_LANES
+// lanes share it, lane l holding the key channels l + GLA_LANES * i in registers, and a block of 128 threads runs 16
+// columns.  The tokens' q (scaled), k, decay and v come into shared memory sixteen (the widest heads: eight) tokens at
+// a time.  Per token a lane does 2 NPER multiply-adds and the lanes' parts of the output are summed by shuffles in a
+// fixed order.  The decay is alpha = exp(log_sigmoid(z + bias) / tau) in float32: formed by every block for its head
+// (z_bias given), or beforehand for all tokens at once (gla_decay_kernel, z_bias null: z holds alpha).
+//
+// Whole requests (seg_len 0), grid (requests, heads, column blocks): a block runs all tokens of its request.
+// Long prompts (seg_len > 0), grid (requests * segments, heads, column blocks), two launches.  A request's tokens are
+// cut into segments of seg_len.  First launch: segment 0 runs from the request's state and writes its outputs; every
+// later segment but the last runs from a zero state without outputs and leaves the state L it ends in and the product
+// D of its decays.  Second launch: segment p >= 1 starts from L_0 carried through the segments in between
+// (S <- D_j S + L_j) and writes its outputs; the last one stores the request's state.  A request of one segment is
+// done by the first launch alone.  L and D of the segment that starts at row r are entry r / seg_len of `seg_state`
+// and `seg_decay` (full segments do not overlap, so neither do their entries).
 // proj: rows [q: H*d | k: H*d | v: H*dv | ...] in T; z: [T, H*d] float32; state: [H][dv][d] floats per slot;
 // o: [T, H*dv] float32.
 constexpr int GLA_TOK_MAX = 16;
 constexpr int GLA_LANES = 8;
 constexpr int GLA_COLS = 128 / GLA_LANES;
+constexpr int GLA_SEG = 128;                                        // tokens in a segment of a long prompt
+
+__global__ void __launch_bounds__(256) gla_decay_kernel(float* __restrict__ z, const float* __restrict__ z_bias, int K,
+                                                        float inv_tau, long long n) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        z[i] = expf(log_sigmoid_f(z[i] + __ldg(z_bias + (int)(i % K))) * inv_tau);
+}
 
 template <typename T, int NPER>
 __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ z,
                                                        const float* __restrict__ z_bias, int H, int d, int dv, float inv_tau,
                                                        float q_scale, float* __restrict__ state, long long state_stride,
                                                        const int* __restrict__ cu_q, const int* __restrict__ slots,
-                                                       float* __restrict__ o) {
+                                                       float* __restrict__ o, int seg_len, int segs, int second,
+                                                       float* __restrict__ seg_state, float* __restrict__ seg_decay) {
     constexpr int ROW = GLA_LANES * NPER;                           // a token's q (or k, or decay), zeros from d on
     constexpr int GLA_TOK = NPER > 16 ? GLA_TOK_MAX / 2 : GLA_TOK_MAX;     // (static shared memory ends at 48 KB)
     __shared__ float qs[GLA_TOK][ROW], ks[GLA_TOK][ROW], as[GLA_TOK][ROW], vs[GLA_TOK][GLA_COLS];
-    const int s = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * GLA_COLS;
+    const int s = seg_len > 0 ? blockIdx.x / segs : blockIdx.x;
+    const int h = blockIdx.y, v0 = blockIdx.z * GLA_COLS;
     const int slot = slots[s];
     const int q0 = cu_q[s], nq = cu_q[s + 1] - q0;
     if (slot < 0 || nq <= 0) return;
+    int p = 0, P = 1, t_begin = 0, t_end = nq;
+    if (seg_len > 0) {
+        P = (nq + seg_len - 1) / seg_len;
+        p = blockIdx.x % segs + (second ? 1 : 0);
+        if (p >= P || (!second && p > 0 && p == P - 1)) return;     // (the last segment belongs to the second launch)
+        t_begin = p * seg_len;
+        t_end = min(nq, t_begin + seg_len);
+    }
+    const bool last = p == P - 1;
+    const bool emit = second || p == 0;
+    const bool track = !second && p > 0;
     const int tid = threadIdx.x, lane = tid & (GLA_LANES - 1), col = tid / GLA_LANES;
     const int v = v0 + col;
     const bool ok = v < dv;
-    float* sp = state + (size_t)slot * state_stride + ((size_t)h * dv + (ok ? v : 0)) * d;
-    float S[NPER];
+    const size_t col_off = ((size_t)h * dv + (ok ? v : 0)) * d, seg_stride = (size_t)H * dv * d;
+    float* sp = state + (size_t)slot * state_stride + col_off;
+    float S[NPER], Dp[NPER];
 #pragma unroll
-    for (int i = 0; i < NPER; ++i) S[i] = ok && lane + GLA_LANES * i < d ? sp[lane + GLA_LANES * i] : 0.f;
+    for (int i = 0; i < NPER; ++i) {
+        const int n = lane + GLA_LANES * i;
+        Dp[i] = 1.f;
+        S[i] = 0.f;
+        if (ok && n < d) {
+            if (p == 0) {
+                S[i] = sp[n];
+            } else if (second) {
+                float acc = seg_state[(size_t)(q0 / seg_len) * seg_stride + col_off + n];
+                for (int j = 1; j < p; ++j) {
+                    const size_t e = (size_t)((q0 + j * seg_len) / seg_len) * seg_stride + col_off + n;
+                    acc = fmaf(seg_decay[e], acc, seg_state[e]);
+                }
+                S[i] = acc;
+            }
+        }
+    }
     const T* q_src = proj + (size_t)h * d;
     const T* k_src = proj + (size_t)H * d + (size_t)h * d;
     const T* v_src = proj + (size_t)2 * H * d + (size_t)h * dv + v0;
     const float* z_src = z + (size_t)h * d;
-    for (int t0 = 0; t0 < nq; t0 += GLA_TOK) {
-        const int nt = min(GLA_TOK, nq - t0);
+    for (int t0 = t_begin; t0 < t_end; t0 += GLA_TOK) {
+        const int nt = min(GLA_TOK, t_end - t0);
         for (int i = tid; i < GLA_TOK * ROW; i += 128) {
             const int t = i / ROW, n = i - t * ROW;
             float qv = 0.f, kv = 0.f, av = 1.f;
@@ -235,7 +313,8 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ pro
                 const size_t row = (size_t)(q0 + t0 + t);
                 qv = to_float(q_src[row * ld + n]) * q_scale;
                 kv = to_float(k_src[row * ld + n]);
-                av = expf(log_sigmoid_f(z_src[row * (size_t)H * d + n] + __ldg(z_bias + h * d + n)) * inv_tau);
+                av = z_src[row * (size_t)H * d + n];
+                if (z_bias != nullptr) av = expf(log_sigmoid_f(av + __ldg(z_bias + h * d + n)) * inv_tau);
             }
             qs[t][n] = qv, ks[t][n] = kv, as[t][n] = av;
         }
@@ -244,55 +323,100 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ pro
             vs[t][c] = t < nt && v0 + c < dv ? to_float(v_src[(size_t)(q0 + t0 + t) * ld + c]) : 0.f;
         }
         __syncthreads();
+        if (emit) {
 #pragma unroll 4
-        for (int t = 0; t < GLA_TOK; ++t) {
-            if (t < nt) {                                           // (uniform over the block)
-                const float vv = vs[t][col];
-                float acc0 = 0.f, acc1 = 0.f;
+            for (int t = 0; t < GLA_TOK; ++t) {
+                if (t < nt) {                                       // (uniform over the block)
+                    const float vv = vs[t][col];
+                    float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-                for (int i = 0; i < NPER; ++i) {
-                    const int n = lane + GLA_LANES * i;
-                    S[i] = fmaf(as[t][n], S[i], ks[t][n] * vv);
-                    if (i & 1) acc1 = fmaf(S[i], qs[t][n], acc1); else acc0 = fmaf(S[i], qs[t][n], acc0);
+                    for (int i = 0; i < NPER; ++i) {
+                        const int n = lane + GLA_LANES * i;
+                        S[i] = fmaf(as[t][n], S[i], ks[t][n] * vv);
+                        if (i & 1) acc1 = fmaf(S[i], qs[t][n], acc1); else acc0 = fmaf(S[i], qs[t][n], acc0);
+                    }
+                    float acc = acc0 + acc1;
+#pragma unroll
+                    for (int m = GLA_LANES / 2; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
+                    if (ok && lane == 0) o[(size_t)(q0 + t0 + t) * H * dv + (size_t)h * dv + v] = acc;
                 }
-                float acc = acc0 + acc1;
+            }
+        } else {
+#pragma unroll 4
+            for (int t = 0; t < GLA_TOK; ++t) {
+                if (t < nt) {
+                    const float vv = vs[t][col];
 #pragma unroll
-                for (int m = GLA_LANES / 2; m >= 1; m >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, m);
-                if (ok && lane == 0) o[(size_t)(q0 + t0 + t) * H * dv + (size_t)h * dv + v] = acc;
+                    for (int i = 0; i < NPER; ++i) {
+                        const int n = lane + GLA_LANES * i;
+                        S[i] = fmaf(as[t][n], S[i], ks[t][n] * vv);
+                        Dp[i] *= as[t][n];
+                    }
+                }
             }
         }
         __syncthreads();
     }
-    if (ok) {
+    if (!ok) return;
+    if (last) {
 #pragma unroll
         for (int i = 0; i < NPER; ++i)
             if (lane + GLA_LANES * i < d) sp[lane + GLA_LANES * i] = S[i];
+    } else if (!second) {
+        const size_t e = (size_t)((q0 + t_begin) / seg_len) * seg_stride + col_off;
+#pragma unroll
+        for (int i = 0; i < NPER; ++i) {
+            const int n = lane + GLA_LANES * i;
+            if (n < d) {
+                seg_state[e + n] = S[i];
+                if (track) seg_decay[e + n] = Dp[i];
+            }
+        }
     }
 }
 
-PL_EXPORT int pl_gla_scan(const void* proj, int dtype, int ld, const float* z, const float* z_bias, int H, int d, int dv,
+// `max_tokens`: no request of the step brings more; `total_tokens`: rows of proj, z and o.  With max_tokens of at least two
+// segments the caller gives `seg_state` and `seg_decay`, each ceil(total_tokens / GLA_SEG) * H * dv * d floats
+// (pl_gla_segment() tells the segment's length); z is then overwritten by the decays.
+PL_EXPORT int pl_gla_segment() { return GLA_SEG; }
+
+PL_EXPORT int pl_gla_scan(const void* proj, int dtype, int ld, float* z, const float* z_bias, int H, int d, int dv,
                           float tau, float q_scale, float* state, long long state_stride, const int* cu_q, const int* slots,
-                          int num_seqs, float* o, cudaStream_t stream) {
+                          int num_seqs, int max_tokens, long long total_tokens, float* seg_state, float* seg_decay, float* o,
+                          cudaStream_t stream) {
     if (num_seqs == 0) return 0;
     PL_REQUIRE(H > 0 && d > 0 && d <= 256 && dv > 0 && tau > 0.f && ld >= 2 * H * d + H * dv,
                "gla_scan: bad sizes H=%d d=%d dv=%d ld=%d (key size at most 256)", H, d, dv, ld);
-    const dim3 grid(num_seqs, H, (dv + GLA_COLS - 1) / GLA_COLS);
+    const bool cut = seg_state != nullptr && seg_decay != nullptr && max_tokens >= 2 * GLA_SEG;
+    const int segs = cut ? (max_tokens + GLA_SEG - 1) / GLA_SEG - 1 : 1;    // blocks per request in each launch
+    const dim3 grid((unsigned)num_seqs * segs, H, (dv + GLA_COLS - 1) / GLA_COLS);
     PL_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gla_scan: %d heads of %d values", H, dv);
     const int nper = (d + GLA_LANES - 1) / GLA_LANES;
-#define PL_GLA(TT, N)                                                                                                     \
-    gla_scan_kernel<TT, N><<<grid, 128, 0, stream>>>((const TT*)proj, ld, z, z_bias, H, d, dv, 1.0f / tau, q_scale, state, \
-                                                     state_stride, cu_q, slots, o)
+    const float* zb = z_bias;
+    if (cut) {
+        const long long n = total_tokens * H * d, blocks = (n + 255) / 256;
+        PL_REQUIRE(total_tokens > 0, "gla_scan: %lld tokens", total_tokens);
+        gla_decay_kernel<<<(unsigned)(blocks < 65535 * 16 ? blocks : 65535 * 16), 256, 0, stream>>>(z, z_bias, H * d, 1.0f / tau, n);
+        PL_LAUNCHED("gla_decay");
+        zb = nullptr;
+    }
+#define PL_GLA(TT, N)                                                                                                      \
+    gla_scan_kernel<TT, N><<<grid, 128, 0, stream>>>((const TT*)proj, ld, z, zb, H, d, dv, 1.0f / tau, q_scale, state,     \
+                                                     state_stride, cu_q, slots, o, cut ? GLA_SEG : 0, segs, second,        \
+                                                     seg_state, seg_decay)
 #define PL_GLA_N(TT)                                                                                        \
     do {                                                                                                    \
         if (nper <= 2) PL_GLA(TT, 2); else if (nper <= 4) PL_GLA(TT, 4); else if (nper <= 8) PL_GLA(TT, 8); \
         else if (nper <= 16) PL_GLA(TT, 16); else PL_GLA(TT, 32);                                           \
     } while (0)
-    if (dtype == PL_F32) PL_GLA_N(float);
-    else if (dtype == PL_BF16) PL_GLA_N(__nv_bfloat16);
-    else return pl_fail("gla_scan: unknown dtype %d", dtype);
+    for (int second = 0; second < (cut ? 2 : 1); ++second) {
+        if (dtype == PL_F32) PL_GLA_N(float);
+        else if (dtype == PL_BF16) PL_GLA_N(__nv_bfloat16);
+        else return pl_fail("gla_scan: unknown dtype %d", dtype);
+        PL_LAUNCHED("gla_scan");
+    }
 #undef PL_GLA_N
 #undef PL_GLA
-    PL_LAUNCHED("gla_scan");
     return 0;
 }
 

@@ -73,20 +73,60 @@ struct StreamNormArgs {
     float eps;
 };
 
-template <typename TB, typename TW, typename TY>
+// VW values in a row at once (VW = 4: one 16-byte or 8-byte access; the pointers are aligned for it)
+template <int VW>
+__device__ __forceinline__ void load_vals(const float* p, float (&v)[VW]) {
+    if (VW == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x, v[VW > 1 ? 1 : 0] = t.y, v[VW > 2 ? 2 : 0] = t.z, v[VW > 3 ? 3 : 0] = t.w;
+    } else {
+        v[0] = p[0];
+    }
+}
+template <int VW>
+__device__ __forceinline__ void load_vals(const __nv_bfloat16* p, float (&v)[VW]) {
+    if (VW == 4) {
+        const uint2 t = *reinterpret_cast<const uint2*>(p);
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+        v[0] = lo.x, v[VW > 1 ? 1 : 0] = lo.y, v[VW > 2 ? 2 : 0] = hi.x, v[VW > 3 ? 3 : 0] = hi.y;
+    } else {
+        v[0] = __bfloat162float(p[0]);
+    }
+}
+template <int VW>
+__device__ __forceinline__ void store_vals(float* p, const float (&v)[VW]) {
+    if (VW == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[VW > 1 ? 1 : 0], v[VW > 2 ? 2 : 0], v[VW > 3 ? 3 : 0]);
+    else p[0] = v[0];
+}
+template <int VW>
+__device__ __forceinline__ void store_vals(__nv_bfloat16* p, const float (&v)[VW]) {
+    if (VW == 4) {
+        uint2 t;
+        *reinterpret_cast<__nv_bfloat162*>(&t.x) = __floats2bfloat162_rn(v[0], v[VW > 1 ? 1 : 0]);
+        *reinterpret_cast<__nv_bfloat162*>(&t.y) = __floats2bfloat162_rn(v[VW > 2 ? 2 : 0], v[VW > 3 ? 3 : 0]);
+        *reinterpret_cast<uint2*>(p) = t;
+    } else {
+        p[0] = __float2bfloat16(v[0]);
+    }
+}
+
+// SMAX: the number of copies this build unrolls for (S <= SMAX); VW: values per access.
+template <typename TB, typename TW, typename TY, int SMAX, int VW>
 __global__ void __launch_bounds__(256) stream_norm_kernel(StreamNormArgs a) {
-    extern __shared__ float u_sh[];                  // [W] the sublayer's input, then [G] the parts' factors
+    extern __shared__ __align__(16) float u_sh[];    // [W] the sublayer's input, [G] the parts' factors, [warps] partial sums
     pdl_launch_dependents();
     const int S = a.S, W = a.W, G = a.G;
     float* fac = u_sh + W;
-    float mix[MAX_STREAMS][MAX_STREAMS], outw[MAX_STREAMS], inw[MAX_STREAMS];
+    float* partial = fac + G;
+    float mix[SMAX][SMAX], outw[SMAX], inw[SMAX];
     // (the connections are weights: older than the kernel in front)
 #pragma unroll
-    for (int s = 0; s < MAX_STREAMS; ++s) {
+    for (int s = 0; s < SMAX; ++s) {
         outw[s] = a.outw != nullptr && s < S ? __ldg(a.outw + s) : 1.f;
         inw[s] = a.inw != nullptr && s < S ? __ldg(a.inw + s) : 1.f;
 #pragma unroll
-        for (int t = 0; t < MAX_STREAMS; ++t)
+        for (int t = 0; t < SMAX; ++t)
             mix[s][t] = a.mix != nullptr && s < S && t < S ? __ldg(a.mix + s * S + t) : (s == t ? 1.f : 0.f);
     }
     pdl_wait();
@@ -94,75 +134,135 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(StreamNormArgs a) {
     float* xr = a.x + r * (size_t)S * W;
     const TB* b1 = a.branch != nullptr ? (const TB*)a.branch + r * W : nullptr;
     const TB* b2 = a.branch2 != nullptr ? (const TB*)a.branch2 + r * W : nullptr;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        float xs[MAX_STREAMS];
+    for (int c = threadIdx.x * VW; c < W; c += blockDim.x * VW) {
+        float xs[SMAX][VW];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s) xs[s] = s < S ? xr[(size_t)s * W + c] : 0.f;
+        for (int s = 0; s < SMAX; ++s) {
+            if (s < S) {
+                load_vals<VW>(xr + (size_t)s * W + c, xs[s]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < VW; ++e) xs[s][e] = 0.f;
+            }
+        }
         if (b1 != nullptr) {
-            float y = to_float(b1[c]);
+            float y[VW];
+            load_vals<VW>(b1 + c, y);
             if (b2 != nullptr || a.bias_a != nullptr) {
-                if (a.bias_a != nullptr) y += __ldg(a.bias_a + c);
-                y *= a.sa;
-                if (b2 != nullptr) {
-                    float y2 = to_float(b2[c]);
-                    if (a.bias_b != nullptr) y2 += __ldg(a.bias_b + c);
-                    y = fmaf(a.sb, y2, y);
+                float y2[VW];
+                if (b2 != nullptr) load_vals<VW>(b2 + c, y2);
+#pragma unroll
+                for (int e = 0; e < VW; ++e) {
+                    if (a.bias_a != nullptr) y[e] += __ldg(a.bias_a + c + e);
+                    y[e] *= a.sa;
+                    if (b2 != nullptr) {
+                        if (a.bias_b != nullptr) y2[e] += __ldg(a.bias_b + c + e);
+                        y[e] = fmaf(a.sb, y2[e], y[e]);
+                    }
                 }
             }
-            float nx[MAX_STREAMS];
+            float nx[SMAX][VW];
 #pragma unroll
-            for (int t = 0; t < MAX_STREAMS; ++t) {
-                float acc = 0.f;
+            for (int t = 0; t < SMAX; ++t) {
 #pragma unroll
-                for (int s = 0; s < MAX_STREAMS; ++s)
-                    if (s < S) acc = fmaf(mix[s][t], xs[s], acc);
-                nx[t] = fmaf(outw[t], y, acc);
+                for (int e = 0; e < VW; ++e) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int s = 0; s < SMAX; ++s)
+                        if (s < S) acc = fmaf(mix[s][t], xs[s][e], acc);
+                    nx[t][e] = fmaf(outw[t], y[e], acc);
+                }
             }
 #pragma unroll
-            for (int t = 0; t < MAX_STREAMS; ++t)
+            for (int t = 0; t < SMAX; ++t)
                 if (t < S) {
-                    xs[t] = nx[t];
-                    xr[(size_t)t * W + c] = nx[t];
+#pragma unroll
+                    for (int e = 0; e < VW; ++e) xs[t][e] = nx[t][e];
+                    store_vals<VW>(xr + (size_t)t * W + c, nx[t]);
                 }
         }
-        float u = 0.f;
+        float u[VW];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s)
-            if (s < S) u = fmaf(inw[s], xs[s], u);
-        u_sh[c] = u;
+        for (int e = 0; e < VW; ++e) {
+            float acc = 0.f;
+#pragma unroll
+            for (int s = 0; s < SMAX; ++s)
+                if (s < S) acc = fmaf(inw[s], xs[s][e], acc);
+            u[e] = acc;
+        }
+        store_vals<VW>(u_sh + c, u);
     }
     __syncthreads();
     if (a.y == nullptr) return;
     const int gw = W / G;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int g = warp; g < G; g += nw) {
+    // few parts: each is cut into `split` pieces, a warp sums a piece and the pieces are added in order
+    const int split = (G < nw && nw % G == 0 && gw % (nw / G) == 0) ? nw / G : 1;
+    if (split > 1) {
+        const int g = warp / split, piece = gw / split, from = g * gw + (warp - g * split) * piece;
         float sq = 0.f;
-        for (int c = lane; c < gw; c += 32) {
-            const float v = u_sh[g * gw + c];
+        for (int c = lane; c < piece; c += 32) {
+            const float v = u_sh[from + c];
             sq = fmaf(v, v, sq);
         }
         sq = warp_sum(sq);
-        if (lane == 0) fac[g] = 1.0f / sqrtf(sq / (float)gw + a.eps);
+        if (lane == 0) partial[warp] = sq;
+        __syncthreads();
+        if (threadIdx.x < G) {
+            float sum = 0.f;
+            for (int k = 0; k < split; ++k) sum += partial[threadIdx.x * split + k];
+            fac[threadIdx.x] = 1.0f / sqrtf(sum / (float)gw + a.eps);
+        }
+    } else {
+        for (int g = warp; g < G; g += nw) {
+            float sq = 0.f;
+            for (int c = lane; c < gw; c += 32) {
+                const float v = u_sh[g * gw + c];
+                sq = fmaf(v, v, sq);
+            }
+            sq = warp_sum(sq);
+            if (lane == 0) fac[g] = 1.0f / sqrtf(sq / (float)gw + a.eps);
+        }
     }
     __syncthreads();
     TY* yr = (TY*)a.y + r * W;
     const TW* w = (const TW*)a.w;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) yr[c] = from_float<TY>(u_sh[c] * fac[c / gw] * to_float(w[c]));
+    for (int c = threadIdx.x * VW; c < W; c += blockDim.x * VW) {
+        float u[VW], wv[VW];
+        load_vals<VW>(u_sh + c, u);
+        load_vals<VW>(w + c, wv);
+#pragma unroll
+        for (int e = 0; e < VW; ++e) u[e] = u[e] * fac[(c + e) / gw] * wv[e];
+        store_vals<VW>(yr + c, u);
+    }
+}
+
+template <typename TB, typename TW, typename TY, int SMAX>
+static int stream_norm_v(const StreamNormArgs& a, bool wide, long long rows, size_t smem, cudaStream_t stream) {
+    if (wide) {
+        if (smem > 48 * 1024)
+            PL_CUDA(cudaFuncSetAttribute(stream_norm_kernel<TB, TW, TY, SMAX, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        PL_CUDA(launch_pdl(stream_norm_kernel<TB, TW, TY, SMAX, 4>, dim3((unsigned)rows), dim3(256), smem, stream, a));
+    } else {
+        if (smem > 48 * 1024)
+            PL_CUDA(cudaFuncSetAttribute(stream_norm_kernel<TB, TW, TY, SMAX, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        PL_CUDA(launch_pdl(stream_norm_kernel<TB, TW, TY, SMAX, 1>, dim3((unsigned)rows), dim3(256), smem, stream, a));
+    }
+    return 0;
+}
+
+template <typename TB, typename TW, typename TY>
+static int stream_norm_s(const StreamNormArgs& a, bool wide, long long rows, size_t smem, cudaStream_t stream) {
+    if (a.S <= 1) return stream_norm_v<TB, TW, TY, 1>(a, wide, rows, smem, stream);
+    if (a.S <= 2) return stream_norm_v<TB, TW, TY, 2>(a, wide, rows, smem, stream);
+    if (a.S <= 4) return stream_norm_v<TB, TW, TY, 4>(a, wide, rows, smem, stream);
+    return stream_norm_v<TB, TW, TY, MAX_STREAMS>(a, wide, rows, smem, stream);
 }
 
 template <typename TB, typename TW>
-static int stream_norm_y(const StreamNormArgs& a, int y_dtype, long long rows, size_t smem, cudaStream_t stream) {
-    if (y_dtype == PL_BF16) {
-        if (smem > 48 * 1024)
-            PL_CUDA(cudaFuncSetAttribute(stream_norm_kernel<TB, TW, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)smem));
-        PL_CUDA(launch_pdl(stream_norm_kernel<TB, TW, __nv_bfloat16>, dim3((unsigned)rows), dim3(256), smem, stream, a));
-    } else {
-        if (smem > 48 * 1024)
-            PL_CUDA(cudaFuncSetAttribute(stream_norm_kernel<TB, TW, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        PL_CUDA(launch_pdl(stream_norm_kernel<TB, TW, float>, dim3((unsigned)rows), dim3(256), smem, stream, a));
-    }
-    return 0;
+static int stream_norm_y(const StreamNormArgs& a, int y_dtype, bool wide, long long rows, size_t smem, cudaStream_t stream) {
+    if (y_dtype == PL_BF16) return stream_norm_s<TB, TW, __nv_bfloat16>(a, wide, rows, smem, stream);
+    return stream_norm_s<TB, TW, float>(a, wide, rows, smem, stream);
 }
 
 PL_EXPORT int pl_stream_norm(float* x, const void* branch, const void* branch2, int branch_dtype, const float* bias_a,
@@ -174,15 +274,18 @@ PL_EXPORT int pl_stream_norm(float* x, const void* branch, const void* branch2, 
                rows, W, S);
     PL_REQUIRE(G >= 1 && W % G == 0, "stream_norm: %d values do not divide into %d parts", W, G);
     PL_REQUIRE(branch2 == nullptr || branch != nullptr, "stream_norm: a second branch without a first");
-    const size_t smem = ((size_t)W + G) * sizeof(float);
+    const size_t smem = ((size_t)W + G + 8) * sizeof(float);
     PL_REQUIRE(smem <= 200 * 1024, "stream_norm: a row of %d values does not fit shared memory", W);
     StreamNormArgs a{x, branch, branch2, bias_a, bias_b, sa, sb, mix, outw, inw, w, y, S, W, G, eps};
+    // four values per access where every row of every operand starts on a 16-byte boundary
+    const uintptr_t all = (uintptr_t)x | (uintptr_t)branch | (uintptr_t)branch2 | (uintptr_t)w | (uintptr_t)y;
+    const bool wide = W % 4 == 0 && all % 16 == 0;
     const bool bf_b = branch != nullptr && branch_dtype == PL_BF16;
     const bool bf_w = w_dtype == PL_BF16;
-    if (bf_b && bf_w) return stream_norm_y<__nv_bfloat16, __nv_bfloat16>(a, y_dtype, rows, smem, stream);
-    if (bf_b) return stream_norm_y<__nv_bfloat16, float>(a, y_dtype, rows, smem, stream);
-    if (bf_w) return stream_norm_y<float, __nv_bfloat16>(a, y_dtype, rows, smem, stream);
-    return stream_norm_y<float, float>(a, y_dtype, rows, smem, stream);
+    if (bf_b && bf_w) return stream_norm_y<__nv_bfloat16, __nv_bfloat16>(a, y_dtype, wide, rows, smem, stream);
+    if (bf_b) return stream_norm_y<__nv_bfloat16, float>(a, y_dtype, wide, rows, smem, stream);
+    if (bf_w) return stream_norm_y<float, __nv_bfloat16>(a, y_dtype, wide, rows, smem, stream);
+    return stream_norm_y<float, float>(a, y_dtype, wide, rows, smem, stream);
 }
 
 // ------------------------------------------------------------------ weighted sum of two branch outputs

@@ -688,7 +688,9 @@ class CudaOps:
     def gated_recurrence(self, gates, b_gates, u, yx, b_in, rate, blocks, taps, state, ctx) -> torch.Tensor:
         """S_t = a S_(t-1) + sqrt(1 - a^2) sigmoid(g_i) u_t with a = exp(rate * sigmoid(g_r)); returns
         S_t * gelu_tanh(yx[:, :C] + b_in[:C]) in the compute dtype.  gates: float32 [T, blocks * 2 * bw], per block
-        [recurrence gate | input gate]; S lives behind the convolution's inputs in the state slot."""
+        [recurrence gate | input gate], overwritten when a request brings more than a few tokens (the decays and drives
+        of all tokens are then formed in place by a kernel of their own, and the scan only multiplies and adds); S lives
+        behind the convolution's inputs in the state slot."""
         lib = load_module("recurrent")
         T, C = u.shape
         ld = yx.shape[1]
@@ -699,24 +701,33 @@ class CudaOps:
                                             self._p(b_in), self._p(rate), C, blocks, self._p(state),
                                             c_longlong(state.shape[1]), c_longlong((taps - 1) * C),
                                             self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), ctx.num_seqs,
-                                            max(int(ctx.max_q_len), 1),
+                                            max(int(ctx.max_q_len), 1), c_longlong(T),
                                             self._p(out), self._stream))
-        self.launches += 1
+        self.launches += 1 if int(ctx.max_q_len) <= 16 else 2
         return out
 
     def linear_attention_scan(self, proj, z, z_bias, H, d, dv, tau, q_scale, state, ctx) -> torch.Tensor:
         """Gated linear attention's recurrence.  proj rows [q: H*d | k: H*d | v: H*dv | ...]; z float32 [T, H*d] the
         decay's pre-activation (bias `z_bias`): alpha = sigmoid(z)^(1/tau); S_t = diag(alpha_t) S_(t-1) + k_t v_t^T,
-        o_t = S_t^T (q_t * q_scale).  state: [slots, H*dv*d] float32, updated in place.  Returns o float32 [T, H*dv]."""
+        o_t = S_t^T (q_t * q_scale).  state: [slots, H*dv*d] float32, updated in place.  Returns o float32 [T, H*dv].
+        z is overwritten by the decays when a request brings a long prompt."""
         lib = load_module("recurrent")
         T, ld = proj.shape
         assert proj.is_contiguous() and z.dtype == torch.float32 and z.is_contiguous() and z.shape == (T, H * d)
         assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == H * dv * d
         o = torch.empty((T, H * dv), dtype=torch.float32, device=self.device)
+        # a long prompt is cut into segments that run side by side: each leaves its end state and the product of its decays
+        seg, longest = lib.pl_gla_segment(), max(int(ctx.max_q_len), 1)
+        cut = longest >= 2 * seg
+        seg_state = seg_decay = None
+        if cut:
+            seg_state = torch.empty((2, -(-T // seg), H * dv * d), dtype=torch.float32, device=self.device)
+            seg_state, seg_decay = seg_state[0], seg_state[1]
         _check(lib, lib.pl_gla_scan(self._p(proj), self._code(proj), ld, self._p(z), self._p(z_bias), H, d, dv, c_float(tau),
                                     c_float(q_scale), self._p(state), c_longlong(state.shape[1]), self._p(ctx.cu_seqlens_q),
-                                    self._p(ctx.state_slots), ctx.num_seqs, self._p(o), self._stream))
-        self.launches += 1
+                                    self._p(ctx.state_slots), ctx.num_seqs, longest, c_longlong(T), self._p(seg_state),
+                                    self._p(seg_decay), self._p(o), self._stream))
+        self.launches += 3 if cut else 1
         return o
 
     def head_norm_gate(self, o, proj, g_col0, H, dv, norm_w, eps) -> torch.Tensor:

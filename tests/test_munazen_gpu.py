@@ -108,9 +108,25 @@ def test_recurrence_mixer_alone(ops, dtype, W, m):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("W,m", [(48, {"heads": 2, "dim": 12, "vdim": 20, "tau": 4.0}), (32, {"heads": 1, "dim": 40, "vdim": 8, "tau": 1.0}),
                                  (24, {"heads": 5, "dim": 4, "vdim": 4, "tau": 16.0}), (64, {"heads": 3, "dim": 128, "vdim": 256, "tau": 16.0}),
-                                 (64, {"heads": 2, "dim": 72, "vdim": 48, "tau": 2.0}), (32, {"heads": 4, "dim": 32, "vdim": 64, "tau": 16.0})])
+                                 (64, {"heads": 2, "dim": 72, "vdim": 48, "tau": 2.0}), (32, {"heads": 4, "dim": 32, "vdim": 48, "tau": 8.0})])
 def test_linear_attention_mixer_alone(ops, dtype, W, m):
     parts.check_gla(ops, "cuda", dtype, W, m, [1, 137, 70, 2], ways=("whole", (0.6, 0.4), "decode", ("every", 2)))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("W,m", [(32, {"heads": 2, "dim": 24, "vdim": 40, "tau": 8.0}), (48, {"heads": 3, "dim": 130, "vdim": 16, "tau": 2.0}),
+                                 (16, {"heads": 1, "dim": 8, "vdim": 33, "tau": 16.0})])
+def test_linear_attention_long_prompts_in_segments(ops, dtype, W, m):
+    """Prompts of two segments and more run their segments side by side: lengths at a segment's edge, one token past
+    it and one short of it, beside short requests, whole and in portions that start inside a segment."""
+    parts.check_gla(ops, "cuda", dtype, W, m, [700, 3, 257, 256, 255, 130, 520],
+                    ways=("whole", (0.45, 0.55), (0.1, 0.9), (0.37, 0.0015, 0.6285)))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("W,m", [(32, {"width": 40, "blocks": 2, "conv": 4}), (24, {"width": 33, "blocks": 1, "conv": 2})])
+def test_recurrence_long_prompts(ops, dtype, W, m):
+    parts.check_recurrence(ops, "cuda", dtype, W, m, [700, 3, 65, 64, 17, 16, 520], ways=("whole", (0.45, 0.55), (0.1, 0.9)))
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
