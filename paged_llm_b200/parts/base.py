@@ -175,6 +175,32 @@ class LazyNormed:
 
 
 @dataclass
+class LazyPair:
+    """A branch output that is the weighted sum of two tensors which has not been formed yet:
+    scales[0] * (a + biases[0]) + scales[1] * (b + biases[1]) in float32 (a mixer of two mixers side by side).  A norm
+    over the copies of the stream takes both in its own kernel (`branch_args`); anything else calls `materialize`."""
+
+    a: torch.Tensor
+    b: torch.Tensor
+    scales: tuple
+    biases: tuple
+
+    def materialize(self, ops) -> torch.Tensor:
+        return ops.scaled_sum(self.a, self.scales[0], self.biases[0], self.b, self.scales[1], self.biases[1])
+
+    def rows(self, ops, idx: torch.Tensor) -> "LazyPair":
+        return LazyPair(ops.gather_rows(self.a, idx), ops.gather_rows(self.b, idx), self.scales, self.biases)
+
+
+def branch_args(branch, ops):
+    """(branch tensor, keyword arguments) for `ops.stream_norm`: a pair travels as two branches with their scales and
+    biases, everything else as one tensor."""
+    if isinstance(branch, LazyPair):
+        return branch.a, dict(branch2=branch.b, scales=branch.scales, biases=branch.biases)
+    return materialize(branch, ops), {}
+
+
+@dataclass
 class StreamBranch:
     """A branch output that several copies of the residual stream are waiting for (hyper-connections): the copies
     become x_t <- sum_s mix[s, t] x_s + out[t] * branch, all at once from the old ones.  `mix` [streams, streams]
@@ -191,7 +217,7 @@ class StreamBranch:
 
 
 def materialize(branch, ops):
-    return branch.materialize(ops) if isinstance(branch, (LazyLinear, LazyNormed)) else branch
+    return branch.materialize(ops) if isinstance(branch, (LazyLinear, LazyNormed, LazyPair)) else branch
 
 
 # --------------------------------------------------------------------------- interfaces

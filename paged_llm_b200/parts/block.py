@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import Block, LazyNormed, StreamBranch, TensorSpec, materialize, register_block
+from .base import Block, LazyNormed, StreamBranch, TensorSpec, branch_args, materialize, register_block
 
 
 @register_block("pre_norm")
@@ -89,8 +89,8 @@ class HyperConnectionBlock(Block):
         if pending is None:
             h = ops.stream_norm(x, self.streams, None, None, None, w_in, norm.weight, norm.groups, norm.eps)
         elif isinstance(pending, StreamBranch):
-            h = ops.stream_norm(x, self.streams, materialize(pending.branch, ops), pending.mix, pending.out, w_in,
-                                norm.weight, norm.groups, norm.eps)
+            y, pair = branch_args(pending.branch, ops)
+            h = ops.stream_norm(x, self.streams, y, pending.mix, pending.out, w_in, norm.weight, norm.groups, norm.eps, **pair)
         else:
             raise TypeError("a layer of several streams follows a layer of one")
         return StreamBranch(part.forward(h, ctx, *args), w_mix, w_out)

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import LazyLinear, LazyNormed, Norm, StreamBranch, TensorSpec, materialize, register_norm
+from .base import LazyLinear, LazyNormed, LazyPair, Norm, StreamBranch, TensorSpec, branch_args, materialize, register_norm
 
 
 @register_norm("rms_norm")
@@ -44,13 +44,14 @@ class RMSNorm(Norm):
             # one kernel: the copies of the stream take the branch in, are summed, and the sum is normed in parts
             ops = ctx.ops
             if isinstance(branch, StreamBranch):
-                return ops.stream_norm(x, self.streams, materialize(branch.branch, ops), branch.mix, branch.out, None,
-                                       self.weight, self.groups, self.eps)
-            y = materialize(branch, ops) if branch is not None else None
-            return ops.stream_norm(x, self.streams, y, None, None, None, self.weight, self.groups, self.eps)
+                y, pair = branch_args(branch.branch, ops)
+                return ops.stream_norm(x, self.streams, y, branch.mix, branch.out, None, self.weight, self.groups, self.eps,
+                                       **pair)
+            y, pair = branch_args(branch, ops) if branch is not None else (None, {})
+            return ops.stream_norm(x, self.streams, y, None, None, None, self.weight, self.groups, self.eps, **pair)
         if branch is None:
             return ctx.ops.rms_norm(x, self.weight, self.eps)
-        if isinstance(branch, LazyLinear) and branch.bias is not None:
+        if isinstance(branch, LazyPair) or (isinstance(branch, LazyLinear) and branch.bias is not None):
             branch = branch.materialize(ctx.ops)
         if isinstance(branch, LazyLinear):
             return ctx.ops.linear_add_rms_norm(branch.input, branch.weight, x, self.weight, self.eps)

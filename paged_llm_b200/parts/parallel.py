@@ -8,7 +8,7 @@ float32 and is formed by one kernel.
 
 from __future__ import annotations
 
-from .base import MIXERS, LazyLinear, Mixer, PartSpec, make_part, register_mixer
+from .base import MIXERS, LazyLinear, LazyPair, Mixer, PartSpec, make_part, register_mixer
 
 
 @register_mixer("parallel")
@@ -56,4 +56,4 @@ class ParallelMixer(Mixer):
                 y, bias = ops.linear(y.input, y.weight), y.bias
             outs.append((y, bias))
         (a, bias_a), (b, bias_b) = outs
-        return ops.scaled_sum(a, self.scales[0], bias_a, b, self.scales[1], bias_b)
+        return LazyPair(a, b, (self.scales[0], self.scales[1]), (bias_a, bias_b))

@@ -33,12 +33,15 @@ class TorchOps:
         self._count("embedding")
         return (table[ids.long()].float() * scale).repeat(1, copies)
 
-    def stream_norm(self, x, streams, branch, mix, out, w_in, norm_w, groups, eps):
+    def stream_norm(self, x, streams, branch, mix, out, w_in, norm_w, groups, eps, branch2=None, scales=None, biases=None):
         self._count("stream_norm")
         rows, width = x.shape[0], x.shape[1] // streams
         xs = x.view(rows, streams, width)
         if branch is not None:
             y = branch.float()
+            if branch2 is not None:
+                (sa, sb), (ba, bb) = scales, biases
+                y = sa * (y + (ba.float() if ba is not None else 0.0)) + sb * (branch2.float() + (bb.float() if bb is not None else 0.0))
             if mix is None:
                 xs += y[:, None, :]
             else:
