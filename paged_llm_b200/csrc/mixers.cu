@@ -487,6 +487,14 @@ struct RotTable {
     int len, rd, inter;
 };
 
+// Blocks of 256 threads per row for kernels that walk a row's elements: one for a step of many rows, up to eight where
+// the rows are few and each thread would otherwise make many dependent passes.
+static inline unsigned row_blocks(int rows, int elements) {
+    if (rows >= 512) return 1;
+    const int want = (elements + 255) / 256;
+    return (unsigned)(want < 1 ? 1 : want > 8 ? 8 : want);
+}
+
 template <typename T>
 __global__ void rotated_qkv_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ bias, T* __restrict__ q_out,
                                    T* __restrict__ kv, SlotArgs sa, RotTable qk, RotTable vt, int nh, int nkv, int d, int dv,
@@ -494,15 +502,17 @@ __global__ void rotated_qkv_kernel(const T* __restrict__ proj, int ld, const flo
     const int t = blockIdx.x;
     const int s = sa.token_seq[t];
     T* qo = q_out + (size_t)t * nh * D;
+    // (a token's elements are spread over the gridDim.y blocks of its row: few tokens, many blocks)
+    const int first = blockIdx.y * blockDim.x + threadIdx.x, step = gridDim.y * blockDim.x;
     if (s < 0) {                                   // a row that pads the step
-        for (int i = threadIdx.x; i < nh * D; i += blockDim.x) qo[i] = from_float<T>(0.f);
+        for (int i = first; i < nh * D; i += step) qo[i] = from_float<T>(0.f);
         return;
     }
     const int pos = sa.positions[t];
     const T* row = proj + (size_t)t * ld;
     const float2* cs_qk = qk.table != nullptr && pos >= 0 && pos < qk.len ? qk.table + (size_t)pos * (qk.rd >> 1) : nullptr;
     const float2* cs_v = vt.table != nullptr && pos >= 0 && pos < vt.len ? vt.table + (size_t)pos * (vt.rd >> 1) : nullptr;
-    for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+    for (int i = first; i < nh * D; i += step) {
         const int h = i / D, c = i - h * D;
         float v = 0.f;
         if (c < d) {
@@ -517,7 +527,7 @@ __global__ void rotated_qkv_kernel(const T* __restrict__ proj, int ld, const flo
     if (slot < 0) return;
     const size_t head_stride = (size_t)sa.ps * D, v_off = (size_t)nkv * sa.ps * D;
     const int k0 = nh * d, v0 = nh * d + nkv * d;
-    for (int i = threadIdx.x; i < nkv * D; i += blockDim.x) {
+    for (int i = first; i < nkv * D; i += step) {
         const int h = i / D, c = i - h * D;
         float kk = 0.f, vv = 0.f;
         if (c < d) {
@@ -547,12 +557,13 @@ PL_EXPORT int pl_rotated_qkv_write(const void* proj, int dtype, int T, int ld, c
                "heads of %d / %d", qk_rd, v_rd, d, dv);
     SlotArgs sa{positions, token_seq, block_table, bt_stride, num_pages, ps};
     RotTable qk{(const float2*)qk_table, qk_len, qk_rd, qk_inter}, vt{(const float2*)v_table, v_len, v_rd, v_inter};
+    const dim3 grid(T, row_blocks(T, nh * D));
     if (dtype == PL_F32)
-        rotated_qkv_kernel<float><<<T, 256, 0, stream>>>((const float*)proj, ld, bias, (float*)q_out, (float*)kv, sa, qk, vt, nh,
-                                                         nkv, d, dv, D, write);
+        rotated_qkv_kernel<float><<<grid, 256, 0, stream>>>((const float*)proj, ld, bias, (float*)q_out, (float*)kv, sa, qk, vt, nh,
+                                                            nkv, d, dv, D, write);
     else if (dtype == PL_BF16)
-        rotated_qkv_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)proj, ld, bias, (__nv_bfloat16*)q_out,
-                                                                 (__nv_bfloat16*)kv, sa, qk, vt, nh, nkv, d, dv, D, write);
+        rotated_qkv_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)proj, ld, bias, (__nv_bfloat16*)q_out,
+                                                                    (__nv_bfloat16*)kv, sa, qk, vt, nh, nkv, d, dv, D, write);
     else
         return pl_fail("rotated_qkv_write: unknown dtype %d", dtype);
     PL_LAUNCHED("rotated_qkv_write");
@@ -573,7 +584,7 @@ __global__ void head_unrotate_gate_kernel(const T* __restrict__ o, int D, const 
     const bool real = token_seq[t] >= 0;
     const float2* cs = real && vt.table != nullptr && pos >= 0 && pos < vt.len ? vt.table + (size_t)pos * (vt.rd >> 1) : nullptr;
     const T* orow = o + (size_t)t * nh * D;
-    for (int i = threadIdx.x; i < nh * dv; i += blockDim.x) {
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < nh * dv; i += gridDim.y * blockDim.x) {
         const int h = i / dv, c = i - h * dv;
         float v = turned(cs, vt.rd, vt.inter, -1.f, c, [&](int e) { return to_float(orow[h * D + e]); });
         if (gate != nullptr) v *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * ldg + h])));
@@ -589,10 +600,10 @@ PL_EXPORT int pl_head_unrotate_gate(const void* o, int dtype, int T, int D, cons
                v_rd);
     RotTable vt{(const float2*)v_table, v_len, v_rd, v_inter};
     if (dtype == PL_F32)
-        PL_CUDA(launch_pdl(head_unrotate_gate_kernel<float>, dim3(T), dim3(256), 0, stream, (const float*)o, D, (const float*)gate,
+        PL_CUDA(launch_pdl(head_unrotate_gate_kernel<float>, dim3(T, row_blocks(T, nh * dv)), dim3(256), 0, stream, (const float*)o, D, (const float*)gate,
                            ldg, positions, token_seq, vt, (float*)out, nh, dv));
     else if (dtype == PL_BF16)
-        PL_CUDA(launch_pdl(head_unrotate_gate_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, (const __nv_bfloat16*)o, D,
+        PL_CUDA(launch_pdl(head_unrotate_gate_kernel<__nv_bfloat16>, dim3(T, row_blocks(T, nh * dv)), dim3(256), 0, stream, (const __nv_bfloat16*)o, D,
                            (const __nv_bfloat16*)gate, ldg, positions, token_seq, vt, (__nv_bfloat16*)out, nh, dv));
     else
         return pl_fail("head_unrotate_gate: unknown dtype %d", dtype);

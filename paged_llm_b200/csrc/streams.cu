@@ -349,43 +349,63 @@ PL_EXPORT int pl_add_bias(void* y, int dtype, const float* bias, long long rows,
 // One block per row of z [rows, F]: out = a z r1 + b z^2 r2 + c z^3 r3 + e with r_k = 1 / sqrt(mean(z^(2k)) + eps).
 // The second pass over the row (the polynomial, by Horner's rule) finds it in the caches.
 
-template <typename T>
+template <typename T, int VW>
 __global__ void __launch_bounds__(256) poly_norm_kernel(const T* __restrict__ z, const float* __restrict__ coef, float eps,
                                                         T* __restrict__ out, int F) {
-    __shared__ float red[32];
+    __shared__ float red[3][8];
     pdl_launch_dependents();
     const float ca = __ldg(coef), cb = __ldg(coef + 1), cc = __ldg(coef + 2), ce = __ldg(coef + 3);
     pdl_wait();
     const T* zr = z + (size_t)blockIdx.x * F;
     T* o = out + (size_t)blockIdx.x * F;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
-    for (int c = threadIdx.x; c < F; c += blockDim.x) {
-        const float v = to_float(zr[c]), v2 = v * v;
-        s2 += v2;
-        s4 = fmaf(v2, v2, s4);
-        s6 = fmaf(v2 * v2, v2, s6);
+    for (int c = threadIdx.x * VW; c < F; c += blockDim.x * VW) {
+        float v[VW];
+        load_vals<VW>(zr + c, v);
+#pragma unroll
+        for (int e = 0; e < VW; ++e) {
+            const float v2 = v[e] * v[e];
+            s2 += v2;
+            s4 = fmaf(v2, v2, s4);
+            s6 = fmaf(v2 * v2, v2, s6);
+        }
     }
-    s2 = block_sum(s2, red);
-    s4 = block_sum(s4, red);
-    s6 = block_sum(s6, red);
+    // the three sums over the block at once: warps first, then the warps' parts in order
+    s2 = warp_sum(s2), s4 = warp_sum(s4), s6 = warp_sum(s6);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) red[0][warp] = s2, red[1][warp] = s4, red[2][warp] = s6;
+    __syncthreads();
+    s2 = s4 = s6 = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s2 += red[0][k], s4 += red[1][k], s6 += red[2][k];
     const float inv = 1.0f / (float)F;
     const float r1 = ca / sqrtf(s2 * inv + eps), r2 = cb / sqrtf(s4 * inv + eps), r3 = cc / sqrtf(s6 * inv + eps);
-    for (int c = threadIdx.x; c < F; c += blockDim.x) {
-        const float v = to_float(zr[c]);
-        o[c] = from_float<T>(fmaf(v, fmaf(v, fmaf(v, r3, r2), r1), ce));
+    for (int c = threadIdx.x * VW; c < F; c += blockDim.x * VW) {
+        float v[VW];
+        load_vals<VW>(zr + c, v);
+#pragma unroll
+        for (int e = 0; e < VW; ++e) v[e] = fmaf(v[e], fmaf(v[e], fmaf(v[e], r3, r2), r1), ce);
+        store_vals<VW>(o + c, v);
     }
+}
+
+template <typename T>
+static int poly_norm_launch(const T* z, const float* coef, float eps, T* out, long long rows, int F, cudaStream_t stream) {
+    // four values per access where every row starts on a 16-byte boundary
+    if (F % 4 == 0 && ((uintptr_t)z | (uintptr_t)out) % 16 == 0)
+        PL_CUDA(launch_pdl(poly_norm_kernel<T, 4>, dim3((unsigned)rows), dim3(256), 0, stream, z, coef, eps, out, F));
+    else
+        PL_CUDA(launch_pdl(poly_norm_kernel<T, 1>, dim3((unsigned)rows), dim3(256), 0, stream, z, coef, eps, out, F));
+    return 0;
 }
 
 PL_EXPORT int pl_poly_norm(const void* z, int dtype, const float* coef, float eps, void* out, long long rows, int F,
                            cudaStream_t stream) {
     if (rows == 0) return 0;
     PL_REQUIRE(rows > 0 && rows < (1ll << 31) && F > 0, "poly_norm: bad sizes rows=%lld F=%d", rows, F);
-    if (dtype == PL_F32)
-        PL_CUDA(launch_pdl(poly_norm_kernel<float>, dim3((unsigned)rows), dim3(256), 0, stream, (const float*)z, coef, eps,
-                           (float*)out, F));
-    else if (dtype == PL_BF16)
-        PL_CUDA(launch_pdl(poly_norm_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(256), 0, stream, (const __nv_bfloat16*)z,
-                           coef, eps, (__nv_bfloat16*)out, F));
+    if (dtype == PL_F32) return poly_norm_launch((const float*)z, coef, eps, (float*)out, rows, F, stream);
+    if (dtype == PL_BF16)
+        return poly_norm_launch((const __nv_bfloat16*)z, coef, eps, (__nv_bfloat16*)out, rows, F, stream);
     else
         return pl_fail("poly_norm: unknown dtype %d", dtype);
     return 0;
