@@ -223,7 +223,7 @@ PL_EXPORT int pl_gated_recurrence(float* gates, const float* b_gates, const floa
 
 // ------------------------------------------------------------------ gated linear attention, the recurrence
 // A column v of a head's state (its d values over the key channels) is independent of the other columns: GLA_LANES
-// lanes share it, lane l holding the key channels l + GLA_LANES * i in registers, and a block of 128 threads runs 16
+// lanes share it, each holding NPER of the key channels in registers (gla_channel), and a block of 128 threads runs 16
 // columns.  The tokens' q (scaled), k, decay and v come into shared memory sixteen (the widest heads: eight) tokens at
 // a time.  Per token a lane does 2 NPER multiply-adds and the lanes' parts of the output are summed by shuffles in a
 // fixed order.  The decay is alpha = exp(log_sigmoid(z + bias) / tau) in float32: formed by every block for its head
@@ -250,6 +250,14 @@ __global__ void __launch_bounds__(256) gla_decay_kernel(float* __restrict__ z, c
         z[i] = expf(log_sigmoid_f(z[i] + __ldg(z_bias + (int)(i % K))) * inv_tau);
 }
 
+// The key channel that value i of lane `lane` stands for.  Wide heads (NPER a multiple of 4): four consecutive channels
+// at a time, so that a lane reads its q, k and decay from shared memory, and its state from memory, 16 bytes at once
+// and the eight lanes of a column cover 128 consecutive bytes.  Narrow heads: channel lane + 8 i.
+template <int NPER>
+__device__ __forceinline__ int gla_channel(int lane, int i) {
+    return NPER % 4 == 0 ? (i >> 2) * (GLA_LANES * 4) + lane * 4 + (i & 3) : lane + GLA_LANES * i;
+}
+
 template <typename T, int NPER>
 __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ z,
                                                        const float* __restrict__ z_bias, int H, int d, int dv, float inv_tau,
@@ -259,7 +267,7 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ pro
                                                        float* __restrict__ seg_state, float* __restrict__ seg_decay) {
     constexpr int ROW = GLA_LANES * NPER;                           // a token's q (or k, or decay), zeros from d on
     constexpr int GLA_TOK = NPER > 16 ? GLA_TOK_MAX / 2 : GLA_TOK_MAX;     // (static shared memory ends at 48 KB)
-    __shared__ float qs[GLA_TOK][ROW], ks[GLA_TOK][ROW], as[GLA_TOK][ROW], vs[GLA_TOK][GLA_COLS];
+    __shared__ __align__(16) float qs[GLA_TOK][ROW], ks[GLA_TOK][ROW], as[GLA_TOK][ROW], vs[GLA_TOK][GLA_COLS];
     const int s = seg_len > 0 ? blockIdx.x / segs : blockIdx.x;
     const int h = blockIdx.y, v0 = blockIdx.z * GLA_COLS;
     const int slot = slots[s];
@@ -284,7 +292,7 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ pro
     float S[NPER], Dp[NPER];
 #pragma unroll
     for (int i = 0; i < NPER; ++i) {
-        const int n = lane + GLA_LANES * i;
+        const int n = gla_channel<NPER>(lane, i);
         Dp[i] = 1.f;
         S[i] = 0.f;
         if (ok && n < d) {
@@ -329,11 +337,26 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ pro
                 if (t < nt) {                                       // (uniform over the block)
                     const float vv = vs[t][col];
                     float acc0 = 0.f, acc1 = 0.f;
+                    if (NPER % 4 == 0) {
 #pragma unroll
-                    for (int i = 0; i < NPER; ++i) {
-                        const int n = lane + GLA_LANES * i;
-                        S[i] = fmaf(as[t][n], S[i], ks[t][n] * vv);
-                        if (i & 1) acc1 = fmaf(S[i], qs[t][n], acc1); else acc0 = fmaf(S[i], qs[t][n], acc0);
+                        for (int i4 = 0; i4 < NPER / 4; ++i4) {
+                            const int n = i4 * (GLA_LANES * 4) + lane * 4;
+                            const float4 a4 = *reinterpret_cast<const float4*>(&as[t][n]);
+                            const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][n]);
+                            const float4 q4 = *reinterpret_cast<const float4*>(&qs[t][n]);
+                            float* S4 = S + i4 * 4;
+                            S4[0] = fmaf(a4.x, S4[0], k4.x * vv), S4[1] = fmaf(a4.y, S4[1], k4.y * vv);
+                            S4[2] = fmaf(a4.z, S4[2], k4.z * vv), S4[3] = fmaf(a4.w, S4[3], k4.w * vv);
+                            acc0 = fmaf(S4[0], q4.x, acc0), acc1 = fmaf(S4[1], q4.y, acc1);
+                            acc0 = fmaf(S4[2], q4.z, acc0), acc1 = fmaf(S4[3], q4.w, acc1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < NPER; ++i) {
+                            const int n = lane + GLA_LANES * i;
+                            S[i] = fmaf(as[t][n], S[i], ks[t][n] * vv);
+                            if (i & 1) acc1 = fmaf(S[i], qs[t][n], acc1); else acc0 = fmaf(S[i], qs[t][n], acc0);
+                        }
                     }
                     float acc = acc0 + acc1;
 #pragma unroll
@@ -348,7 +371,7 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ pro
                     const float vv = vs[t][col];
 #pragma unroll
                     for (int i = 0; i < NPER; ++i) {
-                        const int n = lane + GLA_LANES * i;
+                        const int n = gla_channel<NPER>(lane, i);
                         S[i] = fmaf(as[t][n], S[i], ks[t][n] * vv);
                         Dp[i] *= as[t][n];
                     }
@@ -361,12 +384,12 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ pro
     if (last) {
 #pragma unroll
         for (int i = 0; i < NPER; ++i)
-            if (lane + GLA_LANES * i < d) sp[lane + GLA_LANES * i] = S[i];
+            if (gla_channel<NPER>(lane, i) < d) sp[gla_channel<NPER>(lane, i)] = S[i];
     } else if (!second) {
         const size_t e = (size_t)((q0 + t_begin) / seg_len) * seg_stride + col_off;
 #pragma unroll
         for (int i = 0; i < NPER; ++i) {
-            const int n = lane + GLA_LANES * i;
+            const int n = gla_channel<NPER>(lane, i);
             if (n < d) {
                 seg_state[e + n] = S[i];
                 if (track) seg_decay[e + n] = Dp[i];
