@@ -236,7 +236,7 @@ PL_EXPORT int pl_gated_recurrence(float* gates, const float* b_gates, const floa
 // D of its decays.  Second launch: segment p >= 1 starts from L_0 carried through the segments in between
 // (S <- D_j S + L_j) and writes its outputs; the last one stores the request's state.  A request of one segment is
 // done by the first launch alone.  L and D of the segment that starts at row r are entry r / seg_len of `seg_state`
-// and `seg_decay` (full segments do not overlap, so neither do their entries).
+// (per column) and `seg_decay` (per head and key channel; full segments do not overlap, so neither do their entries).
 // proj: rows [q: H*d | k: H*d | v: H*dv | ...] in T; z: [T, H*d] float32; state: [H][dv][d] floats per slot;
 // o: [T, H*dv] float32.
 constexpr int GLA_TOK_MAX = 16;
@@ -283,7 +283,8 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ pro
     }
     const bool last = p == P - 1;
     const bool emit = second || p == 0;
-    const bool track = !second && p > 0;
+    // (the product of a segment's decays is the same for every column: one column of the head's first block forms it)
+    const bool track = !second && p > 0 && blockIdx.z == 0 && threadIdx.x < GLA_LANES;
     const int tid = threadIdx.x, lane = tid & (GLA_LANES - 1), col = tid / GLA_LANES;
     const int v = v0 + col;
     const bool ok = v < dv;
@@ -296,15 +297,20 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ pro
         Dp[i] = 1.f;
         S[i] = 0.f;
         if (ok && n < d) {
-            if (p == 0) {
-                S[i] = sp[n];
-            } else if (second) {
-                float acc = seg_state[(size_t)(q0 / seg_len) * seg_stride + col_off + n];
-                for (int j = 1; j < p; ++j) {
-                    const size_t e = (size_t)((q0 + j * seg_len) / seg_len) * seg_stride + col_off + n;
-                    acc = fmaf(seg_decay[e], acc, seg_state[e]);
-                }
-                S[i] = acc;
+            if (p == 0) S[i] = sp[n];
+            else if (second) S[i] = seg_state[(size_t)(q0 / seg_len) * seg_stride + col_off + n];
+        }
+    }
+    if (second && ok) {
+        // (segment by segment, all of the lane's values at once: their loads are independent of each other)
+        for (int j = 1; j < p; ++j) {
+            const size_t entry = (size_t)((q0 + j * seg_len) / seg_len);
+            const float* Lj = seg_state + entry * seg_stride + col_off;
+            const float* Dj = seg_decay + (entry * H + h) * d;
+#pragma unroll
+            for (int i = 0; i < NPER; ++i) {
+                const int n = gla_channel<NPER>(lane, i);
+                if (n < d) S[i] = fmaf(Dj[n], S[i], Lj[n]);
             }
         }
     }
@@ -369,11 +375,24 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ pro
             for (int t = 0; t < GLA_TOK; ++t) {
                 if (t < nt) {
                     const float vv = vs[t][col];
+                    if (NPER % 4 == 0) {
 #pragma unroll
-                    for (int i = 0; i < NPER; ++i) {
-                        const int n = gla_channel<NPER>(lane, i);
-                        S[i] = fmaf(as[t][n], S[i], ks[t][n] * vv);
-                        Dp[i] *= as[t][n];
+                        for (int i4 = 0; i4 < NPER / 4; ++i4) {
+                            const int n = i4 * (GLA_LANES * 4) + lane * 4;
+                            const float4 a4 = *reinterpret_cast<const float4*>(&as[t][n]);
+                            const float4 k4 = *reinterpret_cast<const float4*>(&ks[t][n]);
+                            float* S4 = S + i4 * 4;
+                            S4[0] = fmaf(a4.x, S4[0], k4.x * vv), S4[1] = fmaf(a4.y, S4[1], k4.y * vv);
+                            S4[2] = fmaf(a4.z, S4[2], k4.z * vv), S4[3] = fmaf(a4.w, S4[3], k4.w * vv);
+                            if (track) Dp[i4 * 4] *= a4.x, Dp[i4 * 4 + 1] *= a4.y, Dp[i4 * 4 + 2] *= a4.z, Dp[i4 * 4 + 3] *= a4.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < NPER; ++i) {
+                            const int n = lane + GLA_LANES * i;
+                            S[i] = fmaf(as[t][n], S[i], ks[t][n] * vv);
+                            if (track) Dp[i] *= as[t][n];
+                        }
                     }
                 }
             }
@@ -392,7 +411,7 @@ __global__ void __launch_bounds__(128) gla_scan_kernel(const T* __restrict__ pro
             const int n = gla_channel<NPER>(lane, i);
             if (n < d) {
                 seg_state[e + n] = S[i];
-                if (track) seg_decay[e + n] = Dp[i];
+                if (track) seg_decay[((size_t)((q0 + t_begin) / seg_len) * H + h) * d + n] = Dp[i];
             }
         }
     }
