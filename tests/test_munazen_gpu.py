@@ -49,7 +49,8 @@ def close(got, want, dtype, what, rounding=None):
 
 # ---------------------------------------------------------------- kernels and mixers alone
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,W,S,G", [(9, 48, 3, 2), (1, 32, 1, 1), (5, 40, 5, 4), (4, 24, 2, 3), (300, 1024, 4, 8), (70, 2048, 8, 1)])
+@pytest.mark.parametrize("rows,W,S,G", [(9, 48, 3, 2), (1, 32, 1, 1), (5, 40, 5, 4), (4, 24, 2, 3), (300, 1024, 4, 8), (70, 2048, 8, 1),
+                                        (7, 30, 3, 2), (3, 6, 2, 3), (11, 66, 4, 1), (2, 1030, 1, 5)])
 def test_stream_norm_alone(ops, dtype, rows, W, S, G):
     parts.check_stream_norm(ops, "cuda", dtype, rows, W, S, G)
 
