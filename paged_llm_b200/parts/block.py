@@ -72,16 +72,22 @@ class HyperConnectionBlock(Block):
     def tensor_specs(self):
         out = super().tensor_specs()
         s = self.streams
+        # a single copy may come without connections in the checkpoint: they are then all 1, the plain residual sum
+        opt = s == 1
         for w_in, w_out, w_mix in self.names.values():
-            out[w_in] = TensorSpec((s,), role="vector", init="norm")
-            out[w_out] = TensorSpec((s,), role="vector", init="norm")
-            out[w_mix] = TensorSpec((s, s), role="vector", init="identity")
+            out[w_in] = TensorSpec((s,), role="vector", init="norm", optional=opt)
+            out[w_out] = TensorSpec((s,), role="vector", init="norm", optional=opt)
+            out[w_mix] = TensorSpec((s, s), role="vector", init="identity", optional=opt)
         return out
 
     def load(self, tensors):
         super().load(tensors)
+        like = next(iter(tensors.values()))
         for key, names in self.names.items():
-            self.hc[key] = tuple(tensors[n].float().contiguous() for n in names)
+            shapes = ((self.streams,), (self.streams,), (self.streams, self.streams))
+            self.hc[key] = tuple(tensors[n].float().contiguous() if n in tensors
+                                 else torch.ones(shape, dtype=torch.float32, device=like.device)
+                                 for n, shape in zip(names, shapes))
 
     def _sublayer(self, key, norm, part, x, pending, ctx, *args):
         ops = ctx.ops

@@ -370,6 +370,21 @@ def test_layer_by_layer(folders):
         assert (got.double() - want).abs().max() <= 2e-5 * max(1.0, float(want.abs().max())), f"layer run {i}"
 
 
+def test_one_stream_without_connection_tensors(tmp_path):
+    """`streams: 1` over a checkpoint that has no connection tensors is the plain residual sum."""
+    from tests.munazen_cases import draw_weights
+    base = {k: v for k, v in CASE_B.items()}
+    weights = draw_weights(base, 9)
+    with_key = make_folder(tmp_path / "one", dict(base, streams=1), 9, weights=weights)
+    without = make_folder(tmp_path / "none", base, 9, weights=weights)
+    reqs = requests_for(base["vocab"], (7, 33), seed=4)
+    steps, max_tokens = schedules.mixed(reqs, live=2, seed=2)
+    outputs, _ = replay(with_key, steps, max_tokens)
+    got = schedules.collect(steps, outputs)
+    for rid, toks in reqs.items():
+        close(got[rid], plain_logits(without, toks), f"one stream/{rid}", rounding_error(without, toks))
+
+
 def test_state_does_not_leak_between_requests(folders):
     """A slot and pages that are used again start clean: the second request equals itself run alone."""
     reqs = requests_for(CASE_B["vocab"], (40, 37), seed=4)
