@@ -66,6 +66,10 @@ def _register_builtin() -> None:
     from .munazen import MunazenConfig
     if "Munazen" not in ARCHITECTURES:
         register_architecture("Munazen", MunazenConfig, munazen_spec)
+    from ..models.pirerax import pirerax_spec
+    from .pirerax import PireraxConfig
+    if "Pirerax" not in ARCHITECTURES:
+        register_architecture("Pirerax", PireraxConfig, pirerax_spec)
 
 
 _register_builtin()

@@ -5,7 +5,7 @@ from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSI
                    Head, LayerSpec, LazyLinear, LazyNormed, materialize, Mixer, ModelSpec, Norm, PagedKV, Part, PartSpec, PositionEncoding, ScheduleEntry,
                    StreamBranch, TensorSpec, cache_leaves, make_part, register_block, register_embedding, register_feed_forward, register_head, register_mixer, register_norm,
                    register_position_encoding)
-from . import (attention, block, embedding, latent_attention, linear_attention, mlp, norm, parallel, recurrent, rope,  # noqa: F401
+from . import (attention, block, delta_rule, embedding, latent_attention, linear_attention, mlp, norm, parallel, recurrent, rope,  # noqa: F401
                routed_mlp, ssm)  # noqa: F401  (registration)
 
 __all__ = [

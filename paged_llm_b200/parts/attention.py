@@ -135,6 +135,12 @@ class GatedAttention(Mixer):
       added to the scaled score; it is laid out by distance once (`[heads, L]`) and the kernels read that;
     * a sigmoid gate, computed from the mixer's input, on the concatenated heads in front of the output projection.
 
+    Further options, all off by default: `position` (a rotary table: q and k are rotated after their norms),
+    `query_temperature` (coef, every): the normed query at position p is multiplied by
+    1 + coef * ln(floor((p + 1) / every) + 1), so that late queries look harder; `sink`: one learned number per query
+    head (tensor `sink`) whose exponential joins the softmax's denominator, a term without key or value that is
+    neither scaled nor masked and counts once.
+
     `window` w: the query at position p sees keys p-w+1 .. p.  `keep_window`: what the cache has to keep (the
     largest window of the layers that read it; a layer with `shares_cache` has no key and value projections and
     reads the cache of another layer, written with that layer's norm).
@@ -145,7 +151,7 @@ class GatedAttention(Mixer):
     def __init__(self, weights: dict[str, str], hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  value_dim: int, scale: float, eps: float, window: int | None = None, keep_window: int | None = 0,
                  distance_bias: bool = False, bias_far: float = 0.0, bias_rows: int = 32, gate: bool = True,
-                 shares_cache: bool = False):
+                 shares_cache: bool = False, sink: bool = False, position=None, query_temperature=None):
         if num_heads % num_kv_heads:
             raise ValueError(f"num_heads={num_heads} is not a multiple of num_kv_heads={num_kv_heads}")
         self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
@@ -156,6 +162,16 @@ class GatedAttention(Mixer):
         # the table's number of rows is the checkpoint's (`bias_rows` only says how many the random-weights mode draws)
         self.distance_bias, self.bias_far, self.bias_rows = bool(distance_bias), float(bias_far), int(bias_rows)
         self.gate, self.shares_cache = bool(gate), bool(shares_cache)
+        self.has_sink, self.position = bool(sink), position
+        if position is not None and position.rotary_dim > head_dim:
+            raise ValueError(f"a rotation of {position.rotary_dim} elements in heads of {head_dim}")
+        self.query_temperature = None
+        if query_temperature is not None:
+            coef, every = query_temperature
+            if not int(every) >= 1:
+                raise ValueError(f"query_temperature: every={every} must be at least 1")
+            self.query_temperature = (float(coef), int(every))
+        self.sink = None
         self.cache_dim = pad16(max(head_dim, value_dim))
         if self.cache_dim > MAX_HEAD_DIM:
             raise ValueError(f"head sizes {head_dim} / {value_dim}: the attention kernels take heads of at most {MAX_HEAD_DIM}")
@@ -181,9 +197,13 @@ class GatedAttention(Mixer):
             out[self.names["rel"]] = TensorSpec((-1, self.num_heads), role="vector", draw_shape=(self.bias_rows, self.num_heads))
         if self.gate:
             out[self.names["g_proj"]] = TensorSpec((self.num_heads * dv, h))
+        if self.has_sink:
+            out[self.names["sink"]] = TensorSpec((self.num_heads,), role="vector", init="norm_zero")
         return out
 
     def load(self, tensors):
+        if self.has_sink:
+            self.sink = tensors[self.names["sink"]].float().contiguous()
         stack = ["q_proj"] + ([] if self.shares_cache else ["k_proj", "v_proj"]) + (["g_proj"] if self.gate else [])
         self.w_in = torch.cat([tensors[self.names[k]] for k in stack], dim=0).contiguous()
         self.w_o = tensors[self.names["o_proj"]].contiguous()
@@ -209,9 +229,10 @@ class GatedAttention(Mixer):
         block_table = ctx.block_tables[cache.group]
         proj = ops.linear(h, self.w_in)
         q = ops.normed_qkv_write(proj, nh, nkv, d, dv, D, self.q_weight, self.k_weight, self.eps, ctx, cache.kv,
-                                 block_table, has_kv=not self.shares_cache, write=cache.owner and not self.shares_cache)
+                                 block_table, has_kv=not self.shares_cache, write=cache.owner and not self.shares_cache,
+                                 position=self.position, query_temperature=self.query_temperature)
         o = ops.paged_attention(q, nh, nkv, D, cache.kv, block_table, ctx, self.scale, self.window,
-                                dist_bias=self.bias_by_distance)
+                                dist_bias=self.bias_by_distance, sink=self.sink)
         g0 = nh * d + (0 if self.shares_cache else nkv * (d + dv))
         o = ops.head_gate(o, nh, D, dv, proj[:, g0:g0 + nh * dv] if self.gate else None)
         return LazyLinear(o, self.w_o)

@@ -192,6 +192,27 @@ class LazyPair:
         return LazyPair(ops.gather_rows(self.a, idx), ops.gather_rows(self.b, idx), self.scales, self.biases)
 
 
+@dataclass
+class LazyNormedPair:
+    """A branch output that is the weighted sum of two tensors, each first divided by its own root mean square over
+    the row and multiplied by a weight: scales[0] * rms_norm(a) * weights[0] + scales[1] * rms_norm(b) * weights[1],
+    in float32 (a mixer of two mixers side by side whose outputs are normed before they meet).  The RMS norm that
+    consumes the branch does both norms, the residual sum and its own norm in one kernel; anything else calls
+    `materialize`."""
+
+    a: torch.Tensor
+    b: torch.Tensor
+    weights: tuple
+    scales: tuple
+    eps: float
+
+    def materialize(self, ops) -> torch.Tensor:
+        return ops.normed_pair_sum(self.a, self.b, self.weights[0], self.weights[1], self.scales[0], self.scales[1], self.eps)
+
+    def rows(self, ops, idx: torch.Tensor) -> "LazyNormedPair":
+        return LazyNormedPair(ops.gather_rows(self.a, idx), ops.gather_rows(self.b, idx), self.weights, self.scales, self.eps)
+
+
 def branch_args(branch, ops):
     """(branch tensor, keyword arguments) for `ops.stream_norm`: a pair travels as two branches with their scales and
     biases, everything else as one tensor."""
@@ -217,7 +238,7 @@ class StreamBranch:
 
 
 def materialize(branch, ops):
-    return branch.materialize(ops) if isinstance(branch, (LazyLinear, LazyNormed, LazyPair)) else branch
+    return branch.materialize(ops) if isinstance(branch, (LazyLinear, LazyNormed, LazyPair, LazyNormedPair)) else branch
 
 
 # --------------------------------------------------------------------------- interfaces

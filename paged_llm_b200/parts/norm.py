@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import LazyLinear, LazyNormed, LazyPair, Norm, StreamBranch, TensorSpec, branch_args, materialize, register_norm
+from .base import LazyLinear, LazyNormed, LazyNormedPair, LazyPair, Norm, StreamBranch, TensorSpec, branch_args, materialize, register_norm
 
 
 @register_norm("rms_norm")
@@ -51,6 +51,10 @@ class RMSNorm(Norm):
             return ops.stream_norm(x, self.streams, y, None, None, None, self.weight, self.groups, self.eps, **pair)
         if branch is None:
             return ctx.ops.rms_norm(x, self.weight, self.eps)
+        if isinstance(branch, LazyNormedPair):
+            # both norms of the pair, the residual sum and this norm in one kernel
+            return ctx.ops.normed_pair_add_rms_norm(x, branch.a, branch.b, branch.weights[0], branch.weights[1],
+                                                    branch.scales[0], branch.scales[1], branch.eps, self.weight, self.eps)
         if isinstance(branch, LazyPair) or (isinstance(branch, LazyLinear) and branch.bias is not None):
             branch = branch.materialize(ctx.ops)
         if isinstance(branch, LazyLinear):

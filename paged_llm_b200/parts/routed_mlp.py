@@ -5,6 +5,12 @@ softmax over those top_k logits only; y = sum of weight * expert(h), each expert
 feed-forward down(act(gate h) * up h) without bias.  With `shared_size`, a shared expert of the
 same form runs for every token and is added times sigmoid(w_s . h), one number per token.
 
+Options: `scoring` "sigmoid": every expert scores s = sigmoid(z) by itself, the `top_k` largest scores choose, and the
+weights are those scores as they are (not renormalised).  `groups` (count, keep): the experts form `count` equal groups
+of neighbours, a group scores the sum of its `group_score_top` largest scores, and only experts of the `keep` best
+groups can be chosen.  `activation` "swish_clamped" with `activation_limit` L: g = min(gate, L), u = clamp(up, -L, L),
+the expert's inner vector is g * sigmoid(1.702 g) * (u + 1).
+
 The experts' matrices are stacked when the weights are taken ([E, 2F, D] gate over up, and
 [E, D, F]), the shared gate's row rides behind the router's, and the kernel library does the
 rest on the device: no count per expert ever reaches the host, so a step may be captured.
@@ -17,16 +23,35 @@ import torch
 from .base import FeedForward, TensorSpec, register_feed_forward
 from .mlp import ACTIVATIONS
 
+EXPERT_ACTIVATIONS = ACTIVATIONS + ("swish_clamped",)
+
 
 @register_feed_forward("routed_mlp")
 class RoutedMLP(FeedForward):
     def __init__(self, weights: dict[str, str], hidden_size: int, expert_size: int, num_experts: int, top_k: int,
-                 activation: str = "silu", shared_size: int | None = None, shared_activation: str | None = None):
+                 activation: str = "silu", shared_size: int | None = None, shared_activation: str | None = None,
+                 activation_limit: float | None = None, scoring: str = "softmax_top", groups=None,
+                 group_score_top: int = 2):
         if not 1 <= top_k <= num_experts:
             raise ValueError(f"top_k={top_k} of {num_experts} experts")
         for a in (activation, shared_activation or activation):
-            if a not in ACTIVATIONS:
-                raise ValueError(f"activation {a!r} is not implemented ({', '.join(ACTIVATIONS)} only)")
+            if a not in EXPERT_ACTIVATIONS:
+                raise ValueError(f"activation {a!r} is not implemented ({', '.join(EXPERT_ACTIVATIONS)} only)")
+        if activation == "swish_clamped" and not (activation_limit is not None and activation_limit > 0):
+            raise ValueError("the clamped activation needs a positive activation_limit")
+        if shared_size is not None and (shared_activation or activation) not in ACTIVATIONS:
+            raise ValueError(f"a shared expert takes the activations {', '.join(ACTIVATIONS)} only")
+        if scoring not in ("softmax_top", "sigmoid"):
+            raise ValueError(f"scoring {scoring!r} is not implemented (softmax_top and sigmoid only)")
+        if groups is not None:
+            count, keep = (int(g) for g in groups)
+            if count < 1 or num_experts % count or not 1 <= keep <= count or top_k > num_experts // count * keep:
+                raise ValueError(f"{num_experts} experts in {count} groups of which {keep} are kept, top_k={top_k}")
+            if scoring != "sigmoid":
+                raise ValueError("groups of experts are chosen by sigmoid scores")
+            groups = (count, keep, int(group_score_top))
+        self.activation_limit = float(activation_limit) if activation_limit is not None else 0.0
+        self.scoring, self.groups = scoring, groups
         self.hidden_size, self.expert_size, self.num_experts, self.top_k = hidden_size, expert_size, num_experts, top_k
         self.activation, self.shared_size = activation, shared_size
         self.shared_activation = shared_activation or activation
@@ -76,4 +101,5 @@ class RoutedMLP(FeedForward):
 
     def forward(self, h, ctx):
         return ctx.ops.routed_experts(h, self.w_router, self.w_gate_up, self.w_down, self.top_k, self.activation,
-                                      shared=self.shared, shared_activation=self.shared_activation)
+                                      shared=self.shared, shared_activation=self.shared_activation,
+                                      activation_limit=self.activation_limit, scoring=self.scoring, groups=self.groups)

@@ -107,10 +107,13 @@ class TorchOps:
     def silu_mul(self, gate_up):
         return self.act_mul(gate_up, "silu")
 
-    def act_mul(self, gate_up, activation="silu"):
+    def act_mul(self, gate_up, activation="silu", limit=0.0):
         self._count("silu_mul")
         i = gate_up.shape[1] // 2
         g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
+        if activation == "swish_clamped":
+            g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+            return (g * torch.sigmoid(1.702 * g) * (u + 1.0)).to(self.compute_dtype)
         a = g * torch.sigmoid(g) if activation == "silu" else torch.nn.functional.gelu(g, approximate="tanh")
         return (a * u).to(self.compute_dtype)
 
@@ -125,17 +128,29 @@ class TorchOps:
         return self.act_mul(self.linear(h, w_gate_up), activation)
 
     def routed_experts(self, h, w_router, w_gate_up, w_down, top_k, activation="silu", shared=None,
-                       shared_activation="silu"):
+                       shared_activation="silu", activation_limit=0.0, scoring="softmax_top", groups=None):
         self._count("routed_experts")
         E = w_gate_up.shape[0]
         z = h.float() @ w_router.float().T              # (rows behind the experts' and the gate's are padding)
-        top, idx = torch.topk(z[:, :E], top_k, dim=-1)
-        wt = torch.softmax(top, dim=-1)
+        if scoring == "sigmoid":
+            sc = torch.sigmoid(z[:, :E])
+            pick = sc
+            if groups is not None:
+                count, keep, best = groups
+                per = sc.view(-1, count, E // count)
+                group_score = per.topk(min(best, E // count), dim=-1).values.sum(-1)
+                kept = torch.zeros_like(group_score, dtype=torch.bool).scatter_(1, group_score.topk(keep, dim=-1).indices, True)
+                pick = sc.masked_fill(~kept[:, :, None].expand_as(per).reshape(-1, E), -1.0)
+            idx = torch.topk(pick, top_k, dim=-1).indices
+            wt = sc.gather(1, idx)
+        else:
+            top, idx = torch.topk(z[:, :E], top_k, dim=-1)
+            wt = torch.softmax(top, dim=-1)
         y = torch.zeros(h.shape[0], w_down.shape[1], dtype=torch.float32, device=h.device)
         for t in range(h.shape[0]):
             for j in range(top_k):
                 e = int(idx[t, j])
-                inter = self.act_mul(self.linear(h[t:t + 1], w_gate_up[e]), activation)
+                inter = self.act_mul(self.linear(h[t:t + 1], w_gate_up[e]), activation, activation_limit)
                 y[t] += wt[t, j] * self.linear(inter, w_down[e]).float()[0]
         if shared is not None:
             s = self.linear(self.gated_act_linear(h, shared[0], shared_activation), shared[1]).float()
@@ -211,7 +226,7 @@ class TorchOps:
                               pad_tokens=pad_tokens)
 
     def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None,
-                        chunk=None, dist_bias=None):
+                        chunk=None, dist_bias=None, sink=None):
         self._count("paged_attention")
         T = ctx.num_tokens
         q = qkv[:, :nh * d].view(T, nh, d).float()
@@ -247,7 +262,12 @@ class TorchOps:
             if chunk:
                 hidden |= idx[None, :] < (qpos - qpos % chunk)[:, None]
             scores = scores.masked_fill(hidden[None], float("-inf"))
-            o = torch.einsum("hqk,khd->qhd", scores.softmax(-1), v)
+            if sink is not None:
+                # one more term in the denominator, without a value
+                scores = torch.cat([scores, sink.float().cpu()[:, None, None].expand(nh, nq, 1)], dim=-1)
+                o = torch.einsum("hqk,khd->qhd", scores.softmax(-1)[..., :-1], v)
+            else:
+                o = torch.einsum("hqk,khd->qhd", scores.softmax(-1), v)
             out[cu[s]:cu[s + 1]] = o.reshape(nq, nh * d).to(self.compute_dtype)
         return out
 
@@ -323,11 +343,15 @@ class TorchOps:
             out = out * torch.sigmoid(gate.float())[:, :, None]
         return out.reshape(T, nh * dv).to(self.compute_dtype)
 
-    def causal_conv(self, yx, col0, C, b_in, conv_w, conv_b, state, ctx):
+    def causal_conv(self, yx, col0, C, b_in, conv_w, conv_b, state, ctx, activation=None, low=True):
         self._count("causal_conv")
         taps = conv_w.shape[1]
         hist = taps - 1
-        x = yx[:, col0:col0 + C].float() + b_in[col0:col0 + C]
+        x = yx[:, col0:col0 + C].float()
+        if b_in is not None:
+            x = x + b_in[col0:col0 + C]
+        if conv_b is None:
+            conv_b = torch.zeros(C)
         out = torch.zeros(yx.shape[0], C)
         cu = ctx.host.cu
         for s, slot in enumerate(ctx.host.state_slots):
@@ -338,8 +362,53 @@ class TorchOps:
             for j in range(taps):
                 u = u + seq[j:j + nq] * conv_w[:, j][None, :]
             out[cu[s]:cu[s + 1]] = u
+            if hist:
+                state[slot][:hist * C] = seq[nq:].reshape(-1)
+        if activation == "silu":
+            out = out * torch.sigmoid(out)
+        if not low:
+            return out, None
         low = out.to(self.compute_dtype)
         return out, (out if low.dtype == torch.float32 else low)
+
+    def delta_rule_scan(self, u, proj, gate_col0, decay_rate, decay_bias, H, G, d, dv, unit_eps, q_scale, state_off, state, ctx):
+        """u float32 [T, q: G*d | k: G*d | v: H*dv] (convolved, activated); proj columns gate_col0.. hold [beta: H | a: H]."""
+        self._count("delta_rule_scan")
+        T = u.shape[0]
+        q, k = u[:, :G * d].view(T, G, d), u[:, G * d:2 * G * d].view(T, G, d)
+        v = u[:, 2 * G * d:].view(T, H, dv)
+        q = q * torch.rsqrt((q * q).sum(-1, keepdim=True) + unit_eps) * q_scale
+        k = k * torch.rsqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+        beta = torch.sigmoid(proj[:, gate_col0:gate_col0 + H].float())
+        g = torch.exp(decay_rate * torch.nn.functional.softplus(proj[:, gate_col0 + H:gate_col0 + 2 * H].float() + decay_bias))
+        out = torch.zeros(T, H, dv)
+        cu = ctx.host.cu
+        rep = H // G
+        for s, slot in enumerate(ctx.host.state_slots):
+            assert slot >= 0, "a request of a model with state must own a slot"
+            S = state[slot][state_off:state_off + H * dv * d].view(H, dv, d)          # column j of head h: S[h, j, :]
+            for t in range(cu[s], cu[s + 1]):
+                for h in range(H):
+                    kt, qt = k[t, h // rep], q[t, h // rep]
+                    Sh = S[h] * g[t, h]
+                    w = beta[t, h] * (v[t, h] - Sh @ kt)
+                    Sh = Sh + w[:, None] * kt[None, :]
+                    S[h] = Sh
+                    out[t, h] = Sh @ qt
+        return out.reshape(T, H * dv)
+
+    def normed_pair_sum(self, a, b, wa, wb, sa, sb, eps):
+        self._count("normed_pair_sum")
+
+        def normed(x, w):
+            x = x.float()
+            return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w.float()
+
+        return sa * normed(a, wa) + sb * normed(b, wb)
+
+    def normed_pair_add_rms_norm(self, x, a, b, wa, wb, sa, sb, pair_eps, norm_w, eps):
+        x += self.normed_pair_sum(a, b, wa, wb, sa, sb, pair_eps)
+        return self.rms_norm(x, norm_w, eps)
 
     def gated_recurrence(self, gates, b_gates, u, yx, b_in, rate, blocks, taps, state, ctx):
         self._count("gated_recurrence")
@@ -351,7 +420,6 @@ class TorchOps:
         a = torch.exp(rate[None, :] * r)
         drive = torch.sqrt(1.0 - a * a) * i * u
         y = torch.nn.functional.gelu(yx[:, :C].float() + b_in[:C], approximate="tanh")
-        x = yx[:, C:2 * C].float() + b_in[C:]
         out = torch.zeros(T, C)
         cu = ctx.host.cu
         for s, slot in enumerate(ctx.host.state_slots):
@@ -360,9 +428,7 @@ class TorchOps:
             for t in range(cu[s], cu[s + 1]):
                 S.mul_(a[t]).add_(drive[t])
                 out[t] = S * y[t]
-            old = st[:hist * C].view(hist, C)
-            old.copy_(torch.cat([old, x[cu[s]:cu[s + 1]]], dim=0)[-hist:].clone() if hist else old)
-        return out.to(self.compute_dtype)
+        return out.to(self.compute_dtype)          # (the convolution has replaced its inputs in the state already)
 
     def linear_attention_scan(self, proj, z, z_bias, H, d, dv, tau, q_scale, state, ctx):
         self._count("linear_attention_scan")
@@ -391,20 +457,28 @@ class TorchOps:
         return (v.reshape(T, H * dv) * (g * torch.sigmoid(g))).to(self.compute_dtype)
 
     def normed_qkv_write(self, proj, nh, nkv, d, dv, D, q_weight, k_weight, eps, ctx, kv, block_table, has_kv=True,
-                         write=True):
+                         write=True, position=None, query_temperature=None):
         self._count("normed_qkv_write")
         T = proj.shape[0]
         pf = proj.float()
+        pos = ctx.positions.long()
 
         def normed(x, w):
             return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w
 
+        qn = normed(pf[:, :nh * d], q_weight).view(T, nh, d)
+        if position is not None:
+            qn = self._turn(qn, position, pos.clamp(min=0))
+        if query_temperature is not None:
+            coef, every = query_temperature
+            qn = qn * (1.0 + coef * torch.log(torch.floor((pos.float() + 1.0) / every) + 1.0))[:, None, None]
         q = torch.zeros(T, nh, D)
-        q[:, :, :d] = normed(pf[:, :nh * d], q_weight).view(T, nh, d)
+        q[:, :, :d] = qn
         if has_kv and write:
             k = torch.zeros(T, nkv, D)
             v = torch.zeros(T, nkv, D)
-            k[:, :, :d] = normed(pf[:, nh * d:(nh + nkv) * d], k_weight).view(T, nkv, d)
+            kn = normed(pf[:, nh * d:(nh + nkv) * d], k_weight).view(T, nkv, d)
+            k[:, :, :d] = self._turn(kn, position, pos.clamp(min=0)) if position is not None else kn
             v[:, :, :dv] = pf[:, (nh + nkv) * d:(nh + nkv) * d + nkv * dv].view(T, nkv, dv)
             self._write_slots(ctx, kv, block_table, k, v)
         return q.reshape(T, nh * D).to(self.compute_dtype)
@@ -432,8 +506,14 @@ class TorchOps:
         out[..., 1:rd:2] = b * cos + a * sin
         return out
 
+    def _rotate_part(self, x, position, pos):
+        """x [T, heads, n]: the table's pairing over its rotary_dim leading elements."""
+        if position is None:
+            return x
+        return self._turn(x, position, pos) if position.pairing == "half" else self._rotate_pairs(x, position, pos)
+
     def latent_kv_write(self, down, q_rank, kv_rank, rot_dim, D, q_weight, c_weight, eps, position, ctx, kv, block_table,
-                        write=True):
+                        write=True, norm_q=True):
         self._count("latent_kv_write")
         T = down.shape[0]
         df = down.float()
@@ -441,10 +521,10 @@ class TorchOps:
         def normed(x, w):
             return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w
 
-        cq = normed(df[:, :q_rank], q_weight).to(self.compute_dtype)
+        cq = normed(df[:, :q_rank], q_weight).to(self.compute_dtype) if norm_q else None
         if write:
             c = normed(df[:, q_rank:q_rank + kv_rank], c_weight).to(self.compute_dtype).float()
-            kr = self._rotate_pairs(df[:, q_rank + kv_rank:], position, ctx.positions.long())
+            kr = self._rotate_part(df[:, None, q_rank + kv_rank:q_rank + kv_rank + rot_dim], position, ctx.positions.long())[:, 0]
             k = torch.zeros(T, 1, D)
             v = torch.zeros(T, 1, D)
             k[:, 0, :kv_rank] = c
@@ -458,8 +538,8 @@ class TorchOps:
         T = q.shape[0]
         out = torch.zeros(T, nh, D)
         out[:, :, :kv_rank] = q_abs.float().view(T, nh, kv_rank)
-        qr = q.float().view(T, nh, d + rot_dim)[:, :, d:]
-        out[:, :, kv_rank:kv_rank + rot_dim] = self._rotate_pairs(qr, position, ctx.positions.long())
+        qr = q[:, :nh * (d + rot_dim)].float().view(T, nh, d + rot_dim)[:, :, d:]
+        out[:, :, kv_rank:kv_rank + rot_dim] = self._rotate_part(qr, position, ctx.positions.long())
         return out.reshape(T, nh * D).to(self.compute_dtype)
 
     def ssm_mix(self, zx, inner, groups, state_size, heads, head_dim, conv_w, conv_b, dt_bias, a_log, d_skip, norm_w,
