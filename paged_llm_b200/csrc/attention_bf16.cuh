@@ -468,6 +468,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             part[2 + c] = o0;
             part[3 + c] = o1;
         } else if (it.splits <= 1) {
+            L += attn_sink_term2(p, head, M);
             const float inv = L > 0.f ? 1.0f / L : 0.f;
             __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * d + c;
             *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
@@ -506,8 +507,9 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
                 o0 += v.x * f;
                 o1 += v.y * f;
             }
-            const float inv = L > 0.f ? 1.0f / L : 0.f;
             const int tok = R / G, head = kvh * G + R % G;
+            L += attn_sink_term2(p, head, M);
+            const float inv = L > 0.f ? 1.0f / L : 0.f;
             __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * d + c;
             *reinterpret_cast<__nv_bfloat162*>(o) = __floats2bfloat162_rn(o0 * inv, o1 * inv);
         }
@@ -545,6 +547,7 @@ __global__ void __launch_bounds__(32 * MW * NW) attn_bf16_kernel(AttnParams p) {
             L += ml[2 * (R * it.splits + j) + 1] * f;
             ml[2 * (R * it.splits + j)] = f;
         }
+        L += attn_sink_term(p, kvh * G + R % G, M);
         const float inv = L > 0.f ? 1.0f / L : 0.f;
         for (int j = 0; j < it.splits; ++j) ml[2 * (R * it.splits + j)] *= inv;
     }

@@ -103,7 +103,8 @@ __global__ void __launch_bounds__(128) attn_f32_kernel(AttnParams p) {
         const int tok = R / G, head = kvh * G + R % G;
         if (it.splits <= 1) {
             float* o = (float*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * d;
-            const float inv = l[rr] > 0.f ? 1.0f / l[rr] : 0.f;
+            const float lsum = l[rr] + attn_sink_term(p, head, m[rr]);
+            const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
 #pragma unroll
             for (int cc = 0; cc < F32_MAXD / 32; ++cc) {
                 const int c = lane + 32 * cc;
@@ -143,6 +144,7 @@ __global__ void attn_combine_kernel(AttnParams p) {
             const float* part = attn_partial(p, w.y + i, head, j);
             if (part[0] != -INFINITY) L += part[1] * expf(part[0] - M);
         }
+        L += attn_sink_term(p, head, M);
         const float inv = L > 0.f ? 1.0f / L : 0.f;
         TO* o = (TO*)p.out + (size_t)(q0 + i) * p.out_stride + head * d;
         for (int c = threadIdx.x; c < d; c += blockDim.x) {

@@ -257,11 +257,11 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc_kernel(AttnParams p) {
         // the row sum is the sum of the halves' sums
         xmax[half][r] = l_run;
         __syncthreads();
-        const float l_row = l_run + xmax[half ^ 1][r];
-        // every lane takes part in the aligned load; only valid rows store their 32 columns
-        const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
         const int Rc = pos >= 0 ? R : it.row_base;
         const int tok = Rc / G, head = kvh * G + Rc % G;
+        const float l_row = l_run + xmax[half ^ 1][r] + attn_sink_term2(p, head, m_run);
+        // every lane takes part in the aligned load; only valid rows store their 32 columns
+        const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
         __nv_bfloat16* o_row = (__nv_bfloat16*)p.out + (size_t)(it.q0 + tok) * p.out_stride + head * D + half * 32;
         float o[32];
         tmem_ld32(tmem_o, o);
@@ -676,8 +676,9 @@ __global__ void __launch_bounds__(THREADS, 2) attn_tc2_kernel(AttnParams p, cons
             mbar_wait(&pv_done[last & 1], (last >> 1) & 1);
             __syncwarp();
             fence_after_sync();
-            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
             const int tok = R / G, head = kvh * G + R % G;
+            if (pos >= 0) l_run += attn_sink_term2(p, head, m_run);
+            const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
 #pragma unroll
             for (int c = 0; c < PANELS; ++c) {
                 tmem_ld64(tmem_o + c * 64, sv);                      // every thread of the warp takes part in the load

@@ -43,6 +43,16 @@ __device__ __forceinline__ float gelu_tanh_f(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+// act(gate) * up of a gated feed-forward.  act 0: silu(gate) * up; 1: gelu_tanh(gate) * up; 2, the clamped form with
+// a limit L: g = min(gate, L), u = clamp(up, -L, L), g * sigmoid(1.702 g) * (u + 1).
+constexpr float SWISH_CLAMPED_ALPHA = 1.702f;
+__device__ __forceinline__ float gated_act_f(int act, float limit, float gate, float up) {
+    if (act == 2) {
+        const float g = fminf(gate, limit), u = fminf(fmaxf(up, -limit), limit);
+        return g / (1.0f + expf(-SWISH_CLAMPED_ALPHA * g)) * (u + 1.0f);
+    }
+    return (act == 1 ? gelu_tanh_f(gate) : silu_f(gate)) * up;
+}
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -147,7 +157,22 @@ struct AttnParams {
     // distances from dist_len - 1 on share the last entry.
     const float* dist_bias;
     int dist_len;
+    // A sink in the softmax: [nh] float32 or null.  The denominator of head h also holds exp(sink[h]): a term that has
+    // no key and no value, is not scaled, masked or modified, and counts once however the keys are split.
+    const float* sink;
 };
+
+// What the sink adds to a row's sum of exponentials taken relative to the maximum `m` (natural-log units; -inf:
+// the row saw no key).  Split partials are merged first and the sink joins the merged sum.
+__device__ __forceinline__ float attn_sink_term(const AttnParams& p, int head, float m) {
+    if (p.sink == nullptr) return 0.f;
+    return m == -INFINITY ? 1.f : expf(__ldg(p.sink + head) - m);
+}
+// The same with `m2` in base-2 units (scores times log2 e).
+__device__ __forceinline__ float attn_sink_term2(const AttnParams& p, int head, float m2) {
+    if (p.sink == nullptr) return 0.f;
+    return m2 == -INFINITY ? 1.f : exp2f(__ldg(p.sink + head) * 1.4426950408889634f - m2);
+}
 
 // The lowest key position that the query at `pos` may see (the highest is `pos` itself).
 __device__ __forceinline__ int attn_first_key(const AttnParams& p, int pos) {

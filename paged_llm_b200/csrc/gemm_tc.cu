@@ -24,7 +24,8 @@ PL_EXPORT int pl_gemm_tc_act(const void* X, int ldx, const void* W, void* Y, int
 // Grouped: X [cap, K] holds rows sorted by expert in tiles of 256 (tile i belongs to expert tile_expert[i], *n_tiles
 // tiles are in use), W is [experts][N (or 2N for epilogue 2)][K]; Y [cap, ldy] in the order of X.  epi 0, 1 or 2.
 PL_EXPORT int pl_gemm_tc_grouped(const void* X, int ldx, const void* W, void* Y, int ldy, int cap, int N, int K, int epi,
-                                 int act, int experts, const int* n_tiles, const int* tile_expert, cudaStream_t stream) {
+                                 int act, float act_limit, int experts, const int* n_tiles, const int* tile_expert,
+                                 cudaStream_t stream) {
     PL_REQUIRE(experts > 0, "gemm_tc_grouped: experts=%d", experts);
-    return gemm_tc_duo_launch(X, ldx, W, Y, ldy, nullptr, cap, N, K, epi, stream, act, experts, n_tiles, tile_expert);
+    return gemm_tc_duo_launch(X, ldx, W, Y, ldy, nullptr, cap, N, K, epi, stream, act, experts, n_tiles, tile_expert, act_limit);
 }

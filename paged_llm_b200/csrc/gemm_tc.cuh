@@ -22,7 +22,8 @@ struct TcParams {
     int ldy, M, N, K, I;
     int epi;
     int m_tiles, n_tiles;
-    int act;                    // SiLU epilogue: the gate's activation (0 SiLU, 1 the tanh form of GELU)
+    int act;                    // SiLU epilogue: the gate's activation (0 SiLU, 1 the tanh form of GELU, 2 the clamped form)
+    float act_limit;            // the clamped form's limit
     // Grouped form (null / 0: one W for all rows): the rows of X are sorted by expert in tiles of 256, tile mp
     // multiplies the rows of W that start at tile_expert[mp] * expert_rows, and only *m_pairs_dev tiles exist.
     const int* m_pairs_dev;
@@ -72,7 +73,12 @@ __device__ __forceinline__ void tc_drain_row(const TcParams& p, uint32_t acc, in
                             const float up = __bfloat162float(__float2bfloat16_rn(u[q * 8 + 2 * i + e]));
                             // (the fast division: the IEEE one leaves its fast path for a numerator of zero, and the rows
                             // that pad a tile of the grouped form are all zeros: 175 against 96 us for one such product)
-                            o[e] = (p.act == 1 ? gelu_tanh_f(gate) : __fdividef(gate, 1.0f + __expf(-gate))) * up;
+                            if (p.act == 2) {
+                                const float gc = fminf(gate, p.act_limit), uc = fminf(fmaxf(up, -p.act_limit), p.act_limit);
+                                o[e] = __fdividef(gc, 1.0f + __expf(-SWISH_CLAMPED_ALPHA * gc)) * (uc + 1.0f);
+                            } else {
+                                o[e] = (p.act == 1 ? gelu_tanh_f(gate) : __fdividef(gate, 1.0f + __expf(-gate))) * up;
+                            }
                         }
                         w[i] = pack_bf16x2(o[0], o[1]);
                     }

@@ -200,8 +200,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) gemm_tc_duo_kernel(TcParams p, 
 // rows of X are sorted by expert in tiles of 256 (see TcParams); M is the capacity of X.
 int gemm_tc_duo_launch(const void* X, int ldx, const void* W, void* Y, int ldy, float* resid, int M, int N, int K, int epi,
                        cudaStream_t stream, int act = 0, int experts = 0, const int* m_pairs_dev = nullptr,
-                       const int* tile_expert = nullptr) {
-    PL_REQUIRE(act == 0 || act == 1, "gemm_tc_duo: activation %d", act);
+                       const int* tile_expert = nullptr, float act_limit = 0.f) {
+    PL_REQUIRE(act >= 0 && act <= 2 && (act != 2 || act_limit > 0.f), "gemm_tc_duo: activation %d (limit %g)", act, act_limit);
     PL_REQUIRE(experts == 0 || (m_pairs_dev != nullptr && tile_expert != nullptr && M % 256 == 0 && epi != TC_ADD),
                "gemm_tc_duo: the grouped form needs the tile list and a capacity that is a multiple of 256");
     PL_REQUIRE(epi >= TC_BF16 && epi <= TC_ADD, "gemm_tc_duo: epilogue %d", epi);
@@ -227,6 +227,7 @@ int gemm_tc_duo_launch(const void* X, int ldx, const void* W, void* Y, int ldy, 
     p.I = N;
     p.epi = epi;
     p.act = act;
+    p.act_limit = act_limit;
     p.m_pairs_dev = m_pairs_dev;
     p.tile_expert = tile_expert;
     p.m_tiles = ((M + TC_BM - 1) / TC_BM + 1) / 2 * 2;

@@ -157,14 +157,43 @@ __device__ __forceinline__ long long key_slot(const SlotArgs& a, int t, int s, i
     return (((long long)page * 2) * nkv * a.ps + pos % a.ps) * D;
 }
 
+// A head of n elements turned by the angles of one table row `cs` [rd / 2] of (cos, sin): element e < rd is paired
+// with e ^ 1 (interleaved) or with e +- rd / 2 (halves), elements from rd on pass.  `dir` = -1 turns back.
+// `elem(i)` gives element i of the head before the turn.
+template <typename F>
+__device__ __forceinline__ float turned(const float2* cs, int rd, int inter, float dir, int e, F elem) {
+    const float self = elem(e);
+    if (cs == nullptr || e >= rd) return self;
+    const int half = rd >> 1;
+    int i, partner;
+    bool second;
+    if (inter) {
+        i = e >> 1, partner = e ^ 1, second = e & 1;
+    } else {
+        second = e >= half, i = second ? e - half : e, partner = second ? e - half : e + half;
+    }
+    const float2 t = cs[i];
+    const float sn = dir * t.y, other = elem(partner);
+    return second ? fmaf(self, t.x, other * sn) : fmaf(self, t.x, -other * sn);
+}
+
+// A rotary table and how it pairs the elements of a head.
+struct RotTable {
+    const float2* table;    // [len, rd / 2] or null: no rotation
+    int len, rd, inter;
+};
+
 // ------------------------------------------------------------------ norm over whole projections + cache write
 // proj row: [q: nh*d | k: nkv*d | v: nkv*dv | ...] (k and v only with has_kv).  One block per token.
 //   q' = q / sqrt(mean(q^2) + eps) * qw over all nh*d elements at once, the same for k with kw.
+// With a table `rot`, q' and k' are then rotated by the token's position over the table's leading elements of each head.
+// With t_every > 0 the query is multiplied by 1 + t_coef * ln(floor((position + 1) / t_every) + 1).
 // Q out: [T, nh*D], head h at h*D, columns d..D zero.  K and V go to the page slot, padded to D with zeros.
 template <typename T>
 __global__ void normed_qkv_kernel(const T* __restrict__ proj, int ld, const float* __restrict__ qw,
                                   const float* __restrict__ kw, float eps, T* __restrict__ q_out, T* __restrict__ kv,
-                                  SlotArgs sa, int nh, int nkv, int d, int dv, int D, int has_kv, int write, int vec) {
+                                  SlotArgs sa, int nh, int nkv, int d, int dv, int D, int has_kv, int write, int vec,
+                                  RotTable rot, float t_coef, int t_every) {
     __shared__ float red[32];
     const int t = blockIdx.x;
     const int s = sa.token_seq[t];
@@ -180,8 +209,19 @@ __global__ void normed_qkv_kernel(const T* __restrict__ proj, int ld, const floa
         const float v = to_float(row[i]);
         sq += v * v;
     }
-    const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + eps);
-    if (vec) {
+    const int pos = sa.positions[t];
+    float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + eps);
+    if (t_every > 0) rq *= 1.0f + t_coef * logf((float)((max(pos, 0) + 1) / t_every) + 1.0f);
+    const float2* cs = rot.table != nullptr && pos >= 0 && pos < rot.len ? rot.table + (size_t)pos * (rot.rd >> 1) : nullptr;
+    if (cs != nullptr) {
+        for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
+            const int h = i / D, c = i - h * D;
+            const float v = c < d ? turned(cs, rot.rd, rot.inter, 1.f, c, [&](int e) {
+                return to_float(row[h * d + e]) * __ldg(qw + h * d + e);
+            }) * rq : 0.f;
+            qo[i] = from_float<T>(v);
+        }
+    } else if (vec) {
         for (int i = threadIdx.x * 4; i < nh * D; i += blockDim.x * 4) {
             const int h = i / D, c = i - h * D;
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -198,7 +238,7 @@ __global__ void normed_qkv_kernel(const T* __restrict__ proj, int ld, const floa
         }
     }
     if (!has_kv || !write) return;
-    const long long slot = key_slot(sa, t, s, sa.positions[t], nkv, D);
+    const long long slot = key_slot(sa, t, s, pos, nkv, D);
     float sk = 0.f;
     for (int i = threadIdx.x; i < nk; i += blockDim.x) {
         const float v = to_float(row[nq + i]);
@@ -207,6 +247,18 @@ __global__ void normed_qkv_kernel(const T* __restrict__ proj, int ld, const floa
     const float rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + eps);
     if (slot < 0) return;
     const size_t head_stride = (size_t)sa.ps * D, v_off = (size_t)nkv * sa.ps * D;
+    if (cs != nullptr) {
+        for (int i = threadIdx.x; i < nkv * D; i += blockDim.x) {
+            const int h = i / D, c = i - h * D;
+            const float kk = c < d ? turned(cs, rot.rd, rot.inter, 1.f, c, [&](int e) {
+                return to_float(row[nq + h * d + e]) * __ldg(kw + h * d + e);
+            }) * rk : 0.f;
+            const float vv = c < dv ? to_float(row[nq + nk + h * dv + c]) : 0.f;
+            kv[slot + h * head_stride + c] = from_float<T>(kk);
+            kv[slot + v_off + h * head_stride + c] = from_float<T>(vv);
+        }
+        return;
+    }
     if (vec) {
         for (int i = threadIdx.x * 4; i < nkv * D; i += blockDim.x * 4) {
             const int h = i / D, c = i - h * D;
@@ -233,21 +285,25 @@ __global__ void normed_qkv_kernel(const T* __restrict__ proj, int ld, const floa
 PL_EXPORT int pl_normed_qkv_write(const void* proj, int dtype, int T, int ld, const float* qw, const float* kw, float eps,
                                   void* q_out, void* kv, const int* positions, const int* token_seq,
                                   const int* block_table, int bt_stride, int num_pages, int ps, int nh, int nkv, int d,
-                                  int dv, int D, int has_kv, int write, cudaStream_t stream) {
+                                  int dv, int D, int has_kv, int write, const float* rot_table, int rot_len, int rot_rd,
+                                  int rot_inter, float t_coef, int t_every, cudaStream_t stream) {
     if (T == 0) return 0;
     PL_REQUIRE(nh > 0 && nkv > 0 && d > 0 && dv > 0 && D >= d && D >= dv, "normed_qkv_write: bad head sizes d=%d dv=%d D=%d", d,
                dv, D);
+    PL_REQUIRE(rot_table == nullptr || (rot_rd > 0 && rot_rd % 2 == 0 && rot_rd <= d), "normed_qkv_write: %d rotated elements of %d",
+               rot_rd, d);
+    RotTable rot{(const float2*)rot_table, rot_len, rot_rd, rot_inter};
     SlotArgs sa{positions, token_seq, block_table, bt_stride, num_pages, ps};
     // four elements per step where every head, row and pointer allows it
     const int vec = d % 4 == 0 && dv % 4 == 0 && D % 4 == 0 && ld % 4 == 0 &&
                     (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)kv | (uintptr_t)qw | (uintptr_t)kw) & 15) == 0;
     if (dtype == PL_F32)
         normed_qkv_kernel<float><<<T, 256, 0, stream>>>((const float*)proj, ld, qw, kw, eps, (float*)q_out, (float*)kv, sa,
-                                                        nh, nkv, d, dv, D, has_kv, write, vec);
+                                                        nh, nkv, d, dv, D, has_kv, write, vec, rot, t_coef, t_every);
     else if (dtype == PL_BF16)
         normed_qkv_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)proj, ld, qw, kw, eps,
                                                                 (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv, sa, nh, nkv,
-                                                                d, dv, D, has_kv, write, vec);
+                                                                d, dv, D, has_kv, write, vec, rot, t_coef, t_every);
     else
         return pl_fail("normed_qkv_write: unknown dtype %d", dtype);
     PL_LAUNCHED("normed_qkv_write");
@@ -317,37 +373,34 @@ PL_EXPORT int pl_head_gate(const void* o, int dtype, int T, int D, const void* g
 }
 
 // ------------------------------------------------------------------ latent attention
-// Rotation of pairs (2i, 2i+1), i < half, with (cos, sin) of `table` [positions, half]; the rest passes.
-__device__ __forceinline__ float rot_elem(const float2* cs, int half, bool rotate, float self, float partner, int c) {
-    if (!rotate || c >= 2 * half) return self;
-    const float2 t = cs[c >> 1];
-    return (c & 1) ? self * t.x + partner * t.y : self * t.x - partner * t.y;
-}
-
 // down row: [cq: q_rank | c: kv_rank | kr: rot_dim].  One block per token:
 //   cq_out = cq / rms(cq) * qw;  c' = c / rms(c) * cw;  kr' = rotate(kr, position)
 //   key slot  [c' | kr' | 0 ..D),  value slot [c' | 0 ..D)   (one kv head)
 template <typename T>
 __global__ void latent_kv_kernel(const T* __restrict__ down, int ld, const float* __restrict__ qw,
                                  const float* __restrict__ cw, float eps, T* __restrict__ cq_out, T* __restrict__ kv,
-                                 SlotArgs sa, const float2* __restrict__ table, int table_len, int half, int q_rank,
-                                 int kv_rank, int rot_dim, int D, int write) {
+                                 SlotArgs sa, RotTable rot, int q_rank, int kv_rank, int rot_dim, int D, int write,
+                                 int norm_q) {
     __shared__ float red[32];
     const int t = blockIdx.x;
     const int s = sa.token_seq[t];
-    T* cq = cq_out + (size_t)t * q_rank;
+    T* cq = norm_q ? cq_out + (size_t)t * q_rank : nullptr;
     if (s < 0) {
-        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[i] = from_float<T>(0.f);
+        if (norm_q)
+            for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[i] = from_float<T>(0.f);
         return;
     }
     const T* row = down + (size_t)t * ld;
-    float sq = 0.f;
-    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
-        const float v = to_float(row[i]);
-        sq += v * v;
+    if (norm_q) {
+        // (without a query latent the first q_rank columns are the queries themselves and pass as they are)
+        float sq = 0.f;
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) {
+            const float v = to_float(row[i]);
+            sq += v * v;
+        }
+        const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)q_rank + eps);
+        for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[i] = from_float<T>(to_float(row[i]) * rq * __ldg(qw + i));
     }
-    const float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)q_rank + eps);
-    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[i] = from_float<T>(to_float(row[i]) * rq * __ldg(qw + i));
     if (!write) return;
     float sc = 0.f;
     for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) {
@@ -358,8 +411,7 @@ __global__ void latent_kv_kernel(const T* __restrict__ down, int ld, const float
     const int pos = sa.positions[t];
     const long long slot = key_slot(sa, t, s, pos, 1, D);
     if (slot < 0) return;
-    const bool rotate = half > 0 && pos < table_len;
-    const float2* cs = table + (size_t)pos * half;
+    const float2* cs = rot.table != nullptr && pos < rot.len ? rot.table + (size_t)pos * (rot.rd >> 1) : nullptr;
     const T* kr = row + q_rank + kv_rank;
     const size_t v_off = (size_t)sa.ps * D;
     for (int i = threadIdx.x; i < D; i += blockDim.x) {
@@ -367,9 +419,7 @@ __global__ void latent_kv_kernel(const T* __restrict__ down, int ld, const float
         if (i < kv_rank) {
             kk = vv = to_float(from_float<T>(to_float(row[q_rank + i]) * rc * __ldg(cw + i)));
         } else if (i < kv_rank + rot_dim) {
-            const int c = i - kv_rank;
-            const float partner = (c ^ 1) < rot_dim ? to_float(kr[c ^ 1]) : 0.f;
-            kk = rot_elem(cs, half, rotate, to_float(kr[c]), partner, c);
+            kk = turned(cs, rot.rd, rot.inter, 1.f, i - kv_rank, [&](int e) { return to_float(kr[e]); });
         }
         kv[slot + i] = from_float<T>(kk);
         kv[slot + v_off + i] = from_float<T>(vv);
@@ -379,22 +429,20 @@ __global__ void latent_kv_kernel(const T* __restrict__ down, int ld, const float
 PL_EXPORT int pl_latent_kv_write(const void* down, int dtype, int T, int ld, const float* qw, const float* cw, float eps,
                                  void* cq_out, void* kv, const int* positions, const int* token_seq,
                                  const int* block_table, int bt_stride, int num_pages, int ps, const float* table,
-                                 int table_len, int rotary_dims, int q_rank, int kv_rank, int rot_dim, int D, int write,
-                                 cudaStream_t stream) {
+                                 int table_len, int rotary_dims, int rot_inter, int q_rank, int kv_rank, int rot_dim, int D,
+                                 int write, int norm_q, cudaStream_t stream) {
     if (T == 0) return 0;
     PL_REQUIRE(q_rank > 0 && kv_rank > 0 && rot_dim >= 0 && D >= kv_rank + rot_dim, "latent_kv_write: bad sizes");
     PL_REQUIRE(rotary_dims % 2 == 0 && rotary_dims <= rot_dim, "latent_kv_write: %d rotated dimensions of %d", rotary_dims, rot_dim);
     SlotArgs sa{positions, token_seq, block_table, bt_stride, num_pages, ps};
-    const int half = table != nullptr ? rotary_dims / 2 : 0;
+    RotTable rot{rotary_dims > 0 ? (const float2*)table : nullptr, table_len, rotary_dims, rot_inter};
     if (dtype == PL_F32)
         latent_kv_kernel<float><<<T, 128, 0, stream>>>((const float*)down, ld, qw, cw, eps, (float*)cq_out, (float*)kv, sa,
-                                                       (const float2*)table, table_len, half, q_rank, kv_rank, rot_dim, D,
-                                                       write);
+                                                       rot, q_rank, kv_rank, rot_dim, D, write, norm_q);
     else if (dtype == PL_BF16)
         latent_kv_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>((const __nv_bfloat16*)down, ld, qw, cw, eps,
                                                                (__nv_bfloat16*)cq_out, (__nv_bfloat16*)kv, sa,
-                                                               (const float2*)table, table_len, half, q_rank, kv_rank,
-                                                               rot_dim, D, write);
+                                                               rot, q_rank, kv_rank, rot_dim, D, write, norm_q);
     else
         return pl_fail("latent_kv_write: unknown dtype %d", dtype);
     PL_LAUNCHED("latent_kv_write");
@@ -403,12 +451,11 @@ PL_EXPORT int pl_latent_kv_write(const void* down, int dtype, int T, int ld, con
 
 // Q out [T, nh*D]: head h = [q_abs[t, h, 0..kv_rank) | rotate(q[t, h, d..d+rot_dim)) | 0 ..D).
 // q_abs: [T, nh*kv_rank] (the unrotated part of the query multiplied into the key up-projection);
-// q: [T, nh*(d + rot_dim)].
+// q: rows of `ldq` elements whose first nh*(d + rot_dim) are the heads.
 template <typename T>
 __global__ void latent_q_kernel(const T* __restrict__ q_abs, const T* __restrict__ q, T* __restrict__ q_out,
                                 const int* __restrict__ positions, const int* __restrict__ token_seq,
-                                const float2* __restrict__ table, int table_len, int half, int nh, int d, int rot_dim,
-                                int kv_rank, int D) {
+                                RotTable rot, int nh, int d, int rot_dim, int kv_rank, int D, int ldq) {
     const int t = blockIdx.x;
     const int s = token_seq[t];
     T* qo = q_out + (size_t)t * nh * D;
@@ -417,40 +464,36 @@ __global__ void latent_q_kernel(const T* __restrict__ q_abs, const T* __restrict
         return;
     }
     const int pos = positions[t];
-    const bool rotate = half > 0 && pos >= 0 && pos < table_len;
-    const float2* cs = table + (size_t)max(pos, 0) * half;
+    const float2* cs = rot.table != nullptr && pos >= 0 && pos < rot.len ? rot.table + (size_t)pos * (rot.rd >> 1) : nullptr;
     const T* qa = q_abs + (size_t)t * nh * kv_rank;
-    const T* qr = q + (size_t)t * nh * (d + rot_dim);
+    const T* qr = q + (size_t)t * ldq;
     for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
         const int h = i / D, c = i - h * D;
         float v = 0.f;
         if (c < kv_rank) {
             v = to_float(qa[h * kv_rank + c]);
         } else if (c < kv_rank + rot_dim) {
-            const int e = c - kv_rank;
             const T* part = qr + h * (d + rot_dim) + d;
-            const float partner = (e ^ 1) < rot_dim ? to_float(part[e ^ 1]) : 0.f;
-            v = rot_elem(cs, half, rotate, to_float(part[e]), partner, e);
+            v = turned(cs, rot.rd, rot.inter, 1.f, c - kv_rank, [&](int e) { return to_float(part[e]); });
         }
         qo[i] = from_float<T>(v);
     }
 }
 
 PL_EXPORT int pl_latent_q(const void* q_abs, const void* q, int dtype, int T, void* q_out, const int* positions,
-                          const int* token_seq, const float* table, int table_len, int rotary_dims, int nh, int d,
-                          int rot_dim, int kv_rank, int D, cudaStream_t stream) {
+                          const int* token_seq, const float* table, int table_len, int rotary_dims, int rot_inter, int nh,
+                          int d, int rot_dim, int kv_rank, int D, int ldq, cudaStream_t stream) {
     if (T == 0) return 0;
-    PL_REQUIRE(nh > 0 && d > 0 && D >= kv_rank + rot_dim, "latent_q: bad sizes");
-    const int half = table != nullptr ? rotary_dims / 2 : 0;
+    PL_REQUIRE(nh > 0 && d > 0 && D >= kv_rank + rot_dim && ldq >= nh * (d + rot_dim), "latent_q: bad sizes");
+    PL_REQUIRE(rotary_dims % 2 == 0 && rotary_dims <= rot_dim, "latent_q: %d rotated dimensions of %d", rotary_dims, rot_dim);
+    RotTable rot{rotary_dims > 0 ? (const float2*)table : nullptr, table_len, rotary_dims, rot_inter};
     if (dtype == PL_F32)
         latent_q_kernel<float><<<T, 256, 0, stream>>>((const float*)q_abs, (const float*)q, (float*)q_out, positions,
-                                                      token_seq, (const float2*)table, table_len, half, nh, d, rot_dim,
-                                                      kv_rank, D);
+                                                      token_seq, rot, nh, d, rot_dim, kv_rank, D, ldq);
     else if (dtype == PL_BF16)
         latent_q_kernel<__nv_bfloat16><<<T, 256, 0, stream>>>((const __nv_bfloat16*)q_abs, (const __nv_bfloat16*)q,
                                                               (__nv_bfloat16*)q_out, positions, token_seq,
-                                                              (const float2*)table, table_len, half, nh, d, rot_dim,
-                                                              kv_rank, D);
+                                                              rot, nh, d, rot_dim, kv_rank, D, ldq);
     else
         return pl_fail("latent_q: unknown dtype %d", dtype);
     PL_LAUNCHED("latent_q");
@@ -458,34 +501,10 @@ PL_EXPORT int pl_latent_q(const void* q_abs, const void* q, int dtype, int T, vo
 }
 
 // ------------------------------------------------------------------ attention whose values are rotated too
-// A head of n elements turned by the angles of one table row `cs` [rd / 2] of (cos, sin): element e < rd is paired
-// with e ^ 1 (interleaved) or with e +- rd / 2 (halves), elements from rd on pass.  `dir` = -1 turns back.
-// `elem(i)` gives element i of the head before the turn.
-template <typename F>
-__device__ __forceinline__ float turned(const float2* cs, int rd, int inter, float dir, int e, F elem) {
-    const float self = elem(e);
-    if (cs == nullptr || e >= rd) return self;
-    const int half = rd >> 1;
-    int i, partner;
-    bool second;
-    if (inter) {
-        i = e >> 1, partner = e ^ 1, second = e & 1;
-    } else {
-        second = e >= half, i = second ? e - half : e, partner = second ? e - half : e + half;
-    }
-    const float2 t = cs[i];
-    const float sn = dir * t.y, other = elem(partner);
-    return second ? fmaf(self, t.x, other * sn) : fmaf(self, t.x, -other * sn);
-}
-
 // proj row: [q: nh*d | k: nkv*d | v: nkv*dv | ...] with `bias` (float32, the same layout, may be null) added first.
 // q and k are turned by the token's position with the table `qk` (rd_qk elements of each head), v with the table
 // `vt` over rd_v elements.  Q out: [T, nh*D], head h at h*D, columns d..D zero; K and V go to the token's page slot,
 // padded to D with zeros.  One block per token.
-struct RotTable {
-    const float2* table;    // [len, rd / 2] or null: no rotation
-    int len, rd, inter;
-};
 
 // Blocks of 256 threads per row for kernels that walk a row's elements: one for a step of many rows, up to eight where
 // the rows are few and each thread would otherwise make many dependent passes.
@@ -608,4 +627,76 @@ PL_EXPORT int pl_head_unrotate_gate(const void* o, int dtype, int T, int D, cons
     else
         return pl_fail("head_unrotate_gate: unknown dtype %d", dtype);
     return 0;
+}
+
+// ------------------------------------------------------------------ two branches, each normed, then their weighted sum
+// v = sa * a / rms(a) * wa + sb * b / rms(b) * wb  (each root mean square over the row, eps inside the root; float32).
+// With a stream x (float32 [rows, W], updated in place): x += v, then y = x / rms(x) * nw in y's type, all in this one
+// kernel (a block per row; the row's v stays in shared memory between the passes).  Without x: sum_out = v (float32).
+template <typename T, typename TW, typename TY>
+__global__ void __launch_bounds__(256) normed_pair_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                          const float* __restrict__ wa, const float* __restrict__ wb, float sa,
+                                                          float sb, float pair_eps, float* __restrict__ x,
+                                                          float* __restrict__ sum_out, const TW* __restrict__ nw, float eps,
+                                                          TY* __restrict__ y, int W) {
+    extern __shared__ float rowv[];
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * W;
+    float ssa = 0.f, ssb = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float va = to_float(a[base + c]), vb = to_float(b[base + c]);
+        ssa = fmaf(va, va, ssa);
+        ssb = fmaf(vb, vb, ssb);
+    }
+    const float ra = sa / sqrtf(block_sum(ssa, red) / (float)W + pair_eps);
+    const float rb = sb / sqrtf(block_sum(ssb, red) / (float)W + pair_eps);
+    float ssx = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float v = to_float(a[base + c]) * ra * __ldg(wa + c) + to_float(b[base + c]) * rb * __ldg(wb + c);
+        if (x != nullptr) {
+            v += x[base + c];
+            x[base + c] = v;
+            rowv[c] = v;
+            ssx = fmaf(v, v, ssx);
+        } else {
+            sum_out[base + c] = v;
+        }
+    }
+    if (x == nullptr) return;
+    const float rx = 1.0f / sqrtf(block_sum(ssx, red) / (float)W + eps);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) y[base + c] = from_float<TY>(rowv[c] * rx * to_float(nw[c]));
+}
+
+template <typename T, typename TW, typename TY>
+static int launch_normed_pair(const void* a, const void* b, const float* wa, const float* wb, float sa, float sb, float pair_eps,
+                              float* x, float* sum_out, const void* nw, float eps, void* y, long long rows, int W,
+                              cudaStream_t stream) {
+    PL_CUDA(launch_pdl(normed_pair_kernel<T, TW, TY>, dim3((unsigned)rows), dim3(256), x != nullptr ? (size_t)W * 4 : 0, stream,
+                       (const T*)a, (const T*)b, wa, wb, sa, sb, pair_eps, x, sum_out, (const TW*)nw, eps, (TY*)y, W));
+    return 0;
+}
+
+// dtype: of a and b.  x null: sum_out gets the sum; else x is updated and y (y_dtype) gets its norm with nw (nw_dtype).
+PL_EXPORT int pl_normed_pair(const void* a, const void* b, int dtype, const float* wa, const float* wb, float sa, float sb,
+                             float pair_eps, float* x, float* sum_out, const void* nw, int nw_dtype, float eps, void* y,
+                             int y_dtype, long long rows, int W, cudaStream_t stream) {
+    if (rows == 0) return 0;
+    PL_REQUIRE(rows > 0 && rows < (1LL << 31) && W > 0 && W <= 12 * 1024, "normed_pair: bad sizes rows=%lld W=%d", rows, W);
+    PL_REQUIRE((x != nullptr) == (y != nullptr) && (x != nullptr || sum_out != nullptr), "normed_pair: nowhere to write");
+    const int key = (dtype << 2) | (nw_dtype << 1) | y_dtype;
+#define PAIR(T, TW, TY) return launch_normed_pair<T, TW, TY>(a, b, wa, wb, sa, sb, pair_eps, x, sum_out, nw, eps, y, rows, W, stream)
+    switch (key) {
+        case 0: PAIR(float, float, float);
+        case 1: PAIR(float, float, __nv_bfloat16);
+        case 2: PAIR(float, __nv_bfloat16, float);
+        case 3: PAIR(float, __nv_bfloat16, __nv_bfloat16);
+        case 4: PAIR(__nv_bfloat16, float, float);
+        case 5: PAIR(__nv_bfloat16, float, __nv_bfloat16);
+        case 6: PAIR(__nv_bfloat16, __nv_bfloat16, float);
+        case 7: PAIR(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    }
+#undef PAIR
+    return pl_fail("normed_pair: unknown dtypes %d %d %d", dtype, nw_dtype, y_dtype);
 }

@@ -15,7 +15,8 @@
 
 namespace {
 
-__device__ __forceinline__ float act_f(int act, float z) { return act == 1 ? gelu_tanh_f(z) : silu_f(z); }
+// act(gate) * up; activation 2 is the clamped one (common.cuh: gated_act_f).
+__device__ __forceinline__ float act_mul_f(int act, float limit, float g, float u) { return gated_act_f(act, limit, g, u); }
 
 // ------------------------------------------------------------------ the router's choice
 // The logits z[t][0..E) (and, if `shared_gate`, z[t][E], whose sigmoid is the token's factor for the shared
@@ -69,6 +70,96 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
     if (lane < k) {
         top_idx[(size_t)t * k + lane] = chosen_e;
         top_w[(size_t)t * k + lane] = pj / sum;
+    }
+}
+
+// The arg-max of v[0..n) over a warp (among equals the lowest index); every lane gets the result.
+__device__ __forceinline__ void warp_argmax(const float* v, int n, int lane, float& best, int& arg) {
+    best = -INFINITY;
+    arg = 0x7fffffff;
+    for (int e = lane; e < n; e += 32) {
+        const float x = v[e];
+        if (x > best || (x == best && e < arg)) {
+            best = x;
+            arg = e;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ob > best || (ob == best && oa < arg)) {
+            best = ob;
+            arg = oa;
+        }
+    }
+    if (arg >= n) arg = 0;                              // (only if every value left is NaN)
+}
+
+// Choice by sigmoid scores: s = sigmoid(z) per expert; with groups (count > 0) the experts form `count` equal groups
+// of neighbours, a group scores the sum of its `group_top` largest s, and only experts of the `keep` best groups can be
+// chosen; the k largest s among those choose the experts, and the weights are those s as they are.  One warp per token.
+__global__ void __launch_bounds__(128) moe_sigmoid_topk_kernel(const float* __restrict__ z_all, int ldz, int tokens, int E, int k,
+                                                               int count, int keep, int group_top, int* __restrict__ top_idx,
+                                                               float* __restrict__ top_w) {
+    extern __shared__ float z_smem[];                   // per warp: scores [E], what may still be chosen [E], group scores [E]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= tokens) return;
+    float* sc = z_smem + (size_t)warp * 3 * E;
+    float* pick = sc + E;
+    float* gsc = pick + E;
+    const float* src = z_all + (size_t)t * ldz;
+    for (int e = lane; e < E; e += 32) pick[e] = sc[e] = 1.0f / (1.0f + expf(-src[e]));
+    __syncwarp();
+    if (count > 0) {
+        const int size = E / count;
+        // a lane per group: the sum of the group's `group_top` largest scores, taken one after the other
+        for (int g = lane; g < count; g += 32) {
+            float sum = 0.f;
+            int taken[8];                               // group_top <= 8
+            for (int r = 0; r < group_top && r < size; ++r) {
+                float best = -INFINITY;
+                int arg = -1;
+                for (int i = 0; i < size; ++i) {
+                    bool used = false;
+                    for (int q = 0; q < r; ++q) used |= taken[q] == i;
+                    const float x = sc[g * size + i];
+                    if (!used && x > best) {
+                        best = x;
+                        arg = i;
+                    }
+                }
+                taken[r] = arg;
+                sum += best;
+            }
+            gsc[g] = sum;
+        }
+        __syncwarp();
+        // the best groups stay; their score is taken out as they are found, the others' experts cannot be chosen
+        for (int r = 0; r < keep; ++r) {
+            float best;
+            int arg;
+            warp_argmax(gsc, count, lane, best, arg);
+            __syncwarp();
+            if (lane == 0) gsc[arg] = -INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gsc[e / size] != -INFINITY) pick[e] = -1.0f;
+        __syncwarp();
+    }
+    for (int j = 0; j < k; ++j) {
+        float best;
+        int arg;
+        warp_argmax(pick, E, lane, best, arg);
+        __syncwarp();
+        if (lane == 0) {
+            top_idx[(size_t)t * k + j] = arg;
+            top_w[(size_t)t * k + j] = sc[arg];
+            pick[arg] = -INFINITY;
+        }
+        __syncwarp();
     }
 }
 
@@ -126,6 +217,7 @@ struct MoeGemm {
     const int* n_tiles;
     const float* row_scale;     // [pairs] or null: the result of pair i is multiplied by it
     int lda, a_div, ldo, n_pairs, N, K, act;
+    float act_limit;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -245,7 +337,7 @@ __global__ void __launch_bounds__(128) moe_gemm_bf16_kernel(MoeGemm p) {
                 const int col = n0 + wn * WN + 8 * j + 2 * t4 + q;
                 if (col >= p.N) continue;
                 if (GATED) {
-                    const float v = act_f(p.act, acc[0][j][2 * hh + q]) * acc[NB - 1][j][2 * hh + q];
+                    const float v = act_mul_f(p.act, p.act_limit, acc[0][j][2 * hh + q], acc[NB - 1][j][2 * hh + q]);
                     ((__nv_bfloat16*)p.out)[(size_t)id * p.ldo + col] = __float2bfloat16_rn(v);
                 } else {
                     ((float*)p.out)[(size_t)id * p.ldo + col] = acc[0][j][2 * hh + q] * sc;
@@ -307,7 +399,7 @@ __global__ void __launch_bounds__(256) moe_gemm_plain_kernel(MoeGemm p) {
     for (int j = 0; j < 4; ++j) {
         const int col = n0 + c4 + j;
         if (col >= p.N) continue;
-        if (GATED) ((T*)p.out)[(size_t)id * p.ldo + col] = from_float<T>(act_f(p.act, acc[0][j]) * acc[NB - 1][j]);
+        if (GATED) ((T*)p.out)[(size_t)id * p.ldo + col] = from_float<T>(act_mul_f(p.act, p.act_limit, acc[0][j], acc[NB - 1][j]));
         else ((float*)p.out)[(size_t)id * p.ldo + col] = acc[0][j] * sc;
     }
 }
@@ -402,6 +494,20 @@ PL_EXPORT int pl_moe_topk(const float* z, int ldz, int tokens, int E, int k, int
     return 0;
 }
 
+PL_EXPORT int pl_moe_sigmoid_topk(const float* z, int ldz, int tokens, int E, int k, int count, int keep, int group_top,
+                                  int* top_idx, float* top_w, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    PL_REQUIRE(tokens > 0 && E > 0 && k > 0 && k <= E && E <= 1024 && ldz >= E, "moe_sigmoid_topk: tokens=%d experts=%d top=%d",
+               tokens, E, k);
+    PL_REQUIRE(count == 0 || (count > 0 && E % count == 0 && keep >= 1 && keep <= count && group_top >= 1 && group_top <= 8 &&
+                              k <= E / count * keep),
+               "moe_sigmoid_topk: %d groups of which %d stay, scored by their %d best (at most 8)", count, keep, group_top);
+    moe_sigmoid_topk_kernel<<<(tokens + 3) / 4, 128, (size_t)4 * 3 * E * sizeof(float), stream>>>(z, ldz, tokens, E, k, count, keep,
+                                                                                              group_top, top_idx, top_w);
+    PL_LAUNCHED("moe_sigmoid_topk");
+    return 0;
+}
+
 PL_EXPORT int pl_moe_align(const int* top_idx, int n_pairs, int E, int BM, int cap, int* sorted, int* tile_expert,
                            int* n_tiles, int* place, cudaStream_t stream) {
     PL_REQUIRE(n_pairs > 0 && E > 0 && E <= 1024 && (BM == 16 || BM == 64 || BM == 256) && cap % BM == 0,
@@ -426,10 +532,11 @@ PL_EXPORT int pl_moe_gather(const void* A, int lda, int a_div, const int* sorted
 // lda % 8 == 0), which takes BM 16 or 64; the plain form takes BM 16 only.
 PL_EXPORT int pl_moe_gemm(const void* A, int lda, int a_div, const void* W, void* out, int ldo, const int* sorted,
                           const int* tile_expert, const int* n_tiles, const float* row_scale, int n_pairs, int N, int K,
-                          int gated, int act, int dtype, int BM, int max_tiles, int tensor_cores, cudaStream_t stream) {
+                          int gated, int act, float act_limit, int dtype, int BM, int max_tiles, int tensor_cores,
+                          cudaStream_t stream) {
     PL_REQUIRE(n_pairs > 0 && N > 0 && K > 0 && a_div > 0 && max_tiles > 0, "moe_gemm: bad sizes");
-    PL_REQUIRE(act == 0 || act == 1, "moe_gemm: unknown activation %d", act);
-    MoeGemm p = {A, W, out, sorted, tile_expert, n_tiles, row_scale, lda, a_div, ldo, n_pairs, N, K, act};
+    PL_REQUIRE(act >= 0 && act <= 2 && (act != 2 || act_limit > 0.f), "moe_gemm: unknown activation %d (limit %g)", act, act_limit);
+    MoeGemm p = {A, W, out, sorted, tile_expert, n_tiles, row_scale, lda, a_div, ldo, n_pairs, N, K, act, act_limit};
     if (tensor_cores) {
         PL_REQUIRE(dtype == PL_BF16 && K % 8 == 0 && lda % 8 == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0,
                    "moe_gemm: the tensor-core form takes bfloat16 with K and lda multiples of 8");

@@ -1,11 +1,13 @@
 // Mixers that carry a state of fixed size from token to token, in float32:
 //
 //  * a causal convolution per channel over a projection's columns (bias on the input, bias on the output, no
-//    activation), whose last taps-1 inputs are part of the request's state;
+//    activation or silu), whose last taps-1 inputs are part of the request's state;
 //  * a real-gated linear recurrence per channel:
 //        a = exp(rate * sigmoid(g_r)),   S_t = a S_(t-1) + sqrt(1 - a^2) * sigmoid(g_i) * u_t,   out = S_t * gelu_tanh(y_t)
 //  * gated linear attention, a matrix state per head with a decay per key channel:
 //        alpha = exp(log_sigmoid(z) / tau),   S_t = diag(alpha_t) S_(t-1) + k_t v_t^T,   o_t = S_t^T q_t
+//  * the gated delta rule, a matrix state per head:
+//        S <- g S;   w = beta (v - S^T k);   S <- S + k w^T;   o = S^T q
 //  * the norm of each head's output over its value size, times silu(gate).
 //
 // Every request of the step brings its next tokens (one when it decodes, many in a prompt portion); its state lives
@@ -29,7 +31,7 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ 
                                                           const float* __restrict__ cb, int taps, float* __restrict__ state,
                                                           long long state_stride, const int* __restrict__ cu_q,
                                                           const int* __restrict__ slots, float* __restrict__ u,
-                                                          T* __restrict__ u_low) {
+                                                          T* __restrict__ u_low, int act) {
     const int s = blockIdx.x;
     const int slot = slots[s];
     const int q0 = cu_q[s], nq = cu_q[s + 1] - q0;
@@ -40,14 +42,15 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ 
     const bool ok = c < C;
     float* st = state + (size_t)slot * state_stride;
     const int hist = taps - 1;
-    const float bi = ok ? __ldg(b_in + col0 + c) : 0.f;
+    const float bi = ok && b_in != nullptr ? __ldg(b_in + col0 + c) : 0.f;
     const T* col = in + (size_t)q0 * ld + col0 + (ok ? c : 0);
     auto input = [&](int src) { return src >= 0 ? to_float(col[(size_t)src * ld]) + bi : st[(size_t)(hist + src) * C + c]; };
     if (ok) {
-        const float bias = __ldg(cb + c);
+        const float bias = cb != nullptr ? __ldg(cb + c) : 0.f;
         for (int t = t_lo + lane_t; t < t_hi; t += 8) {
             float acc = bias;
             for (int k = 0; k < taps; ++k) acc = fmaf(__ldg(cw + (size_t)c * taps + k), input(t - hist + k), acc);
+            if (act == 1) acc = acc / (1.0f + expf(-acc));          // silu
             u[(size_t)(q0 + t) * C + c] = acc;
             if (u_low != nullptr) u_low[(size_t)(q0 + t) * C + c] = from_float<T>(acc);
         }
@@ -67,18 +70,20 @@ __global__ void __launch_bounds__(256) causal_conv_kernel(const T* __restrict__ 
 // `max_tokens`: no request of the step brings more.  u: [T, C] float32; u_low: the same in `dtype`, or null.
 PL_EXPORT int pl_causal_conv(const void* in, int dtype, int ld, int col0, int C, const float* b_in, const float* cw,
                              const float* cb, int taps, float* state, long long state_stride, const int* cu_q,
-                             const int* slots, int num_seqs, int max_tokens, float* u, void* u_low, cudaStream_t stream) {
+                             const int* slots, int num_seqs, int max_tokens, float* u, void* u_low, int act,
+                             cudaStream_t stream) {
     if (num_seqs == 0) return 0;
+    PL_REQUIRE(act == 0 || act == 1, "causal_conv: unknown activation %d", act);
     PL_REQUIRE(C > 0 && taps >= 1 && taps <= CONV_TOK && max_tokens >= 1 && col0 >= 0 && col0 + C <= ld,
                "causal_conv: bad sizes C=%d taps=%d col0=%d ld=%d", C, taps, col0, ld);
     const dim3 grid(num_seqs, (C + 31) / 32, (max_tokens + CONV_TOK - 1) / CONV_TOK);
     PL_REQUIRE(grid.z <= 65535 && grid.y <= 65535, "causal_conv: %d tokens, %d channels in a step", max_tokens, C);
     if (dtype == PL_F32)
         causal_conv_kernel<float><<<grid, 256, 0, stream>>>((const float*)in, ld, col0, C, b_in, cw, cb, taps, state, state_stride,
-                                                            cu_q, slots, u, (float*)u_low);
+                                                            cu_q, slots, u, (float*)u_low, act);
     else if (dtype == PL_BF16)
         causal_conv_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)in, ld, col0, C, b_in, cw, cb, taps,
-                                                                    state, state_stride, cu_q, slots, u, (__nv_bfloat16*)u_low);
+                                                                    state, state_stride, cu_q, slots, u, (__nv_bfloat16*)u_low, act);
     else
         return pl_fail("causal_conv: unknown dtype %d", dtype);
     PL_LAUNCHED("causal_conv");
@@ -459,6 +464,163 @@ PL_EXPORT int pl_gla_scan(const void* proj, int dtype, int ld, float* z, const f
     }
 #undef PL_GLA_N
 #undef PL_GLA
+    return 0;
+}
+
+// ------------------------------------------------------------------ gated delta rule
+// u: float32 [T, q: G*d | k: G*d | v: H*dv], convolved and activated.  The first kernel makes q and k unit vectors per
+// head in place (x / sqrt(sum x^2 + unit_eps); q also times q_scale) and forms, per token and value head,
+// beta = sigmoid(b) and g = exp(rate * softplus(a + bias)) from the projection's columns [b: H | a: H] at gate_col0:
+// bg[t] = [beta: H | g: H].  One warp per (token, q/k head) and one thread per (token, value head).
+template <typename T>
+__global__ void __launch_bounds__(256) delta_prepare_kernel(float* __restrict__ u, int C, const T* __restrict__ proj, int ld,
+                                                            int gate_col0, const float* __restrict__ rate,
+                                                            const float* __restrict__ bias, int H, int G, int d,
+                                                            float unit_eps, float q_scale, float* __restrict__ bg,
+                                                            long long tokens) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long units = tokens * 2 * G;                         // (token, q or k, head)
+    for (long long w = (long long)blockIdx.x * 8 + warp; w < units; w += (long long)gridDim.x * 8) {
+        const long long t = w / (2 * G);
+        const int part = (int)(w - t * 2 * G);                      // 0..G-1: q heads, G..2G-1: k heads
+        float* x = u + t * C + (size_t)part * d;
+        float ss = 0.f;
+        for (int i = lane; i < d; i += 32) ss = fmaf(x[i], x[i], ss);
+        ss = warp_sum(ss);
+        const float r = (1.0f / sqrtf(ss + unit_eps)) * (part < G ? q_scale : 1.0f);
+        for (int i = lane; i < d; i += 32) x[i] *= r;
+    }
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < tokens * H; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / H;
+        const int h = (int)(i - t * H);
+        const float b = to_float(proj[t * ld + gate_col0 + h]), a = to_float(proj[t * ld + gate_col0 + H + h]) + __ldg(bias + h);
+        const float sp = a > 20.f ? a : log1pf(expf(a));             // softplus
+        bg[t * 2 * H + h] = sigmoid_f(b);
+        bg[t * 2 * H + H + h] = expf(__ldg(rate + h) * sp);
+    }
+}
+
+// The recurrence.  grid: (requests, value heads, blocks of DR_COLS columns).  A column j of a head's state (the d
+// numbers S[:, j]) is independent of the other columns: DR_LANES lanes share it, lane l holding the key channels
+// 4 l + 32 m + (0..3), m < NPER / 4, in registers.  Per token, with the dots summed over the lanes by a butterfly:
+//     a = g (S_j . k),  c = g (S_j . q),  w = beta (v_j - a),  S_j <- g S_j + k w,  o_j = c + (q . k) w
+// q, k, v, beta and g of DR_TOK tokens at a time are staged in shared memory.  The order of every sum is fixed, so
+// a position's result is bit for bit the same however the prompt was cut and whatever else is in the batch.
+// State of a request, `state_off` floats into its slot: [H][dv][d].
+constexpr int DR_LANES = 8, DR_COLS = 16, DR_TOK = 16;
+
+template <int NPER>
+__global__ void __launch_bounds__(DR_LANES * DR_COLS) delta_scan_kernel(const float* __restrict__ u, int C, const float* __restrict__ bg,
+                                                                       int H, int G, int d, int dv, float* __restrict__ state,
+                                                                       long long state_stride, long long state_off,
+                                                                       const int* __restrict__ cu_q, const int* __restrict__ slots,
+                                                                       float* __restrict__ out) {
+    constexpr int DP = NPER * DR_LANES;                             // padded key size
+    __shared__ __align__(16) float qs[DR_TOK][DP], ks[DR_TOK][DP];
+    __shared__ float vs[DR_TOK][DR_COLS], bs[DR_TOK], gs[DR_TOK];
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int slot = slots[s];
+    const int q0 = cu_q[s], nq = cu_q[s + 1] - q0;
+    if (slot < 0 || nq <= 0) return;
+    const int tid = threadIdx.x, lane = tid % DR_LANES, col = tid / DR_LANES;
+    const int j = blockIdx.z * DR_COLS + col;
+    const bool live = j < dv;
+    const int kvh = h / (H / G);
+    float* sp = state + (size_t)slot * state_stride + state_off + ((size_t)h * dv + (live ? j : 0)) * d;
+    float S[NPER];
+#pragma unroll
+    for (int r = 0; r < NPER; ++r) {
+        const int ch = (r >> 2) * 32 + lane * 4 + (r & 3);
+        S[r] = live && ch < d ? sp[ch] : 0.f;
+    }
+    const float* uq = u + (size_t)q0 * C + (size_t)kvh * d;
+    const float* uk = uq + (size_t)G * d;
+    const float* uv = u + (size_t)q0 * C + (size_t)2 * G * d + (size_t)h * dv + blockIdx.z * DR_COLS;
+    for (int t0 = 0; t0 < nq; t0 += DR_TOK) {
+        const int nt = min(DR_TOK, nq - t0);
+        __syncthreads();
+        for (int e = tid; e < nt * DP; e += DR_LANES * DR_COLS) {
+            const int tt = e / DP, ch = e - tt * DP;
+            qs[tt][ch] = ch < d ? uq[(size_t)(t0 + tt) * C + ch] : 0.f;
+            ks[tt][ch] = ch < d ? uk[(size_t)(t0 + tt) * C + ch] : 0.f;
+        }
+        for (int e = tid; e < nt * DR_COLS; e += DR_LANES * DR_COLS) {
+            const int tt = e / DR_COLS, c = e - tt * DR_COLS;
+            vs[tt][c] = blockIdx.z * DR_COLS + c < dv ? uv[(size_t)(t0 + tt) * C + c] : 0.f;
+        }
+        if (tid < nt) {
+            bs[tid] = bg[(size_t)(q0 + t0 + tid) * 2 * H + h];
+            gs[tid] = bg[(size_t)(q0 + t0 + tid) * 2 * H + H + h];
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            float kr[NPER], qr[NPER];
+#pragma unroll
+            for (int m = 0; m < NPER / 4; ++m) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][m * 32 + lane * 4]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][m * 32 + lane * 4]);
+                kr[4 * m] = k4.x, kr[4 * m + 1] = k4.y, kr[4 * m + 2] = k4.z, kr[4 * m + 3] = k4.w;
+                qr[4 * m] = q4.x, qr[4 * m + 1] = q4.y, qr[4 * m + 2] = q4.z, qr[4 * m + 3] = q4.w;
+            }
+            float a = 0.f, c = 0.f, qk = 0.f;                      // (q . k does not wait for the state)
+#pragma unroll
+            for (int r = 0; r < NPER; ++r) {
+                a = fmaf(S[r], kr[r], a);
+                c = fmaf(S[r], qr[r], c);
+                qk = fmaf(qr[r], kr[r], qk);
+            }
+#pragma unroll
+            for (int o = DR_LANES / 2; o > 0; o >>= 1) {
+                a += __shfl_xor_sync(0xffffffffu, a, o);
+                c += __shfl_xor_sync(0xffffffffu, c, o);
+                qk += __shfl_xor_sync(0xffffffffu, qk, o);
+            }
+            const float g = gs[tt];
+            const float w = bs[tt] * (vs[tt][col] - g * a);
+#pragma unroll
+            for (int r = 0; r < NPER; ++r) S[r] = fmaf(kr[r], w, g * S[r]);
+            if (live && lane == 0) out[(size_t)(q0 + t0 + tt) * H * dv + (size_t)h * dv + j] = fmaf(qk, w, g * c);
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < NPER; ++r) {
+            const int ch = (r >> 2) * 32 + lane * 4 + (r & 3);
+            if (ch < d) sp[ch] = S[r];
+        }
+    }
+}
+
+// out: float32 [T, H*dv].  bg: scratch float32 [T, 2H].  u is overwritten (q and k become unit vectors).
+PL_EXPORT int pl_delta_rule(float* u, int C, const void* proj, int dtype, int ld, int gate_col0, const float* rate,
+                            const float* bias, int H, int G, int d, int dv, float unit_eps, float q_scale, float* bg,
+                            float* state, long long state_stride, long long state_off, const int* cu_q, const int* slots,
+                            int num_seqs, long long tokens, float* out, cudaStream_t stream) {
+    if (num_seqs == 0 || tokens == 0) return 0;
+    PL_REQUIRE(H > 0 && G > 0 && H % G == 0 && d > 0 && dv > 0 && C == 2 * G * d + H * dv, "delta_rule: bad sizes H=%d G=%d d=%d dv=%d C=%d",
+               H, G, d, dv, C);
+    PL_REQUIRE(d <= 32 * DR_LANES, "delta_rule: key size %d above %d", d, 32 * DR_LANES);
+    PL_REQUIRE(gate_col0 >= 0 && gate_col0 + 2 * H <= ld, "delta_rule: gate columns outside the row");
+    const long long units = tokens * 2 * G;
+    const unsigned pb = (unsigned)min((units + 7) / 8 > tokens * H / 256 + 1 ? (units + 7) / 8 : tokens * H / 256 + 1, 8192LL);
+    if (dtype == PL_F32)
+        delta_prepare_kernel<float><<<pb, 256, 0, stream>>>(u, C, (const float*)proj, ld, gate_col0, rate, bias, H, G, d, unit_eps,
+                                                            q_scale, bg, tokens);
+    else if (dtype == PL_BF16)
+        delta_prepare_kernel<__nv_bfloat16><<<pb, 256, 0, stream>>>(u, C, (const __nv_bfloat16*)proj, ld, gate_col0, rate, bias, H, G,
+                                                                    d, unit_eps, q_scale, bg, tokens);
+    else
+        return pl_fail("delta_rule: unknown dtype %d", dtype);
+    PL_LAUNCHED("delta_prepare");
+    const dim3 grid(num_seqs, H, (dv + DR_COLS - 1) / DR_COLS);
+    PL_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "delta_rule: %d heads of %d values", H, dv);
+#define DELTA_SCAN(N) delta_scan_kernel<N><<<grid, DR_LANES * DR_COLS, 0, stream>>>(u, C, bg, H, G, d, dv, state, state_stride, state_off, cu_q, slots, out)
+    if (d <= 4 * DR_LANES) DELTA_SCAN(4);
+    else if (d <= 8 * DR_LANES) DELTA_SCAN(8);
+    else if (d <= 16 * DR_LANES) DELTA_SCAN(16);
+    else DELTA_SCAN(32);
+#undef DELTA_SCAN
+    PL_LAUNCHED("delta_scan");
     return 0;
 }
 

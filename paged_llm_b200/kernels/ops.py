@@ -46,10 +46,14 @@ class AttnParams(ctypes.Structure):
         ("scale", c_float), ("ps_shift", c_int), ("counters", c_void_p), ("num_pages", c_int), ("cluster", c_int),
         ("softcap", c_float), ("slopes", c_void_p), ("rope_table", c_void_p), ("rope_len", c_int),
         ("pad_seqs", c_int), ("pad_to", c_int), ("chunk", c_int), ("dist_bias", c_void_p), ("dist_len", c_int),
+        ("sink", c_void_p),
     ]
 
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}       # codes of the gate's activation in the kernels
+# the routed experts' kernels also take the clamped form with a limit L:
+# g = min(gate, L), u = clamp(up, -L, L), g * sigmoid(1.702 g) * (u + 1)
+EXPERT_ACTIVATIONS = dict(ACTIVATIONS, swish_clamped=2)
 
 
 def attention_plan_key(num_heads: int, num_kv_heads: int, window, head_dim: int, chunk=None) -> tuple:
@@ -470,18 +474,22 @@ class CudaOps:
         return torch.bmm(xv, w.transpose(1, 2)).transpose(0, 1).reshape(T, nh * N)
 
     def normed_qkv_write(self, proj, nh, nkv, d, dv, D, q_weight, k_weight, eps, ctx, kv, block_table, has_kv=True,
-                         write=True) -> torch.Tensor:
+                         write=True, position=None, query_temperature=None) -> torch.Tensor:
         """proj rows [q: nh*d | k: nkv*d | v: nkv*dv | ...]: q and k are each divided by the root mean square
         of the whole projection (all heads at once) and multiplied by their weights; returns the queries as
         [T, nh*D] (heads padded to D with zeros) and writes keys and values, padded the same way, to their page
-        slots.  Without `has_kv` the rows hold no k and v (the layer reads another layer's cache)."""
+        slots.  Without `has_kv` the rows hold no k and v (the layer reads another layer's cache).  `position` (a
+        prepared rotary encoding): q and k are rotated after their norms.  `query_temperature` (coef, every): the
+        query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)."""
         T, ld = proj.shape
         assert proj.is_contiguous() and kv.is_contiguous() and kv.dtype == proj.dtype and kv.shape[4] == D
         q = torch.empty((T, nh * D), dtype=proj.dtype, device=self.device)
         _check(self.core, self.core.pl_normed_qkv_write(
             self._p(proj), self._code(proj), T, ld, self._p(q_weight), self._p(k_weight), c_float(eps), self._p(q),
             self._p(kv), self._p(ctx.positions), self._p(ctx.token_seq), self._p(block_table), block_table.shape[1],
-            kv.shape[0], kv.shape[3], nh, nkv, d, dv, D, 1 if has_kv else 0, 1 if write else 0, self._stream))
+            kv.shape[0], kv.shape[3], nh, nkv, d, dv, D, 1 if has_kv else 0, 1 if write else 0, *self._rot_args(position),
+            c_float(query_temperature[0] if query_temperature else 0.0), int(query_temperature[1]) if query_temperature else 0,
+            self._stream))
         self.launches += 1
         return q
 
@@ -501,34 +509,32 @@ class CudaOps:
         return out
 
     def latent_kv_write(self, down, q_rank, kv_rank, rot_dim, D, q_weight, c_weight, eps, position, ctx, kv, block_table,
-                        write=True) -> torch.Tensor:
+                        write=True, norm_q=True):
         """down rows [query latent: q_rank | key/value latent: kv_rank | rotated key part: rot_dim]: both latents
         are RMS-normed (float32) with their weights; the normed query latent is returned [T, q_rank]; the cache
-        (one kv head of size D) gets the key [latent | rotated part | 0] and the value [latent | 0]."""
+        (one kv head of size D) gets the key [latent | rotated part | 0] and the value [latent | 0].  Without `norm_q`
+        the first q_rank columns are not a latent (the queries themselves, projected straight from the input): they
+        are left alone and nothing is returned."""
         T, ld = down.shape
         assert down.is_contiguous() and kv.is_contiguous() and kv.dtype == down.dtype and kv.shape[4] == D and kv.shape[2] == 1
-        cq = torch.empty((T, q_rank), dtype=down.dtype, device=self.device)
-        table = position.table if position is not None else None
+        cq = torch.empty((T, q_rank), dtype=down.dtype, device=self.device) if norm_q else None
         _check(self.core, self.core.pl_latent_kv_write(
             self._p(down), self._code(down), T, ld, self._p(q_weight), self._p(c_weight), c_float(eps), self._p(cq),
             self._p(kv), self._p(ctx.positions), self._p(ctx.token_seq), self._p(block_table), block_table.shape[1],
-            kv.shape[0], kv.shape[3], self._p(table), table.shape[0] if table is not None else 0,
-            position.rotary_dim if position is not None else 0, q_rank, kv_rank, rot_dim, D, 1 if write else 0,
-            self._stream))
+            kv.shape[0], kv.shape[3], *self._rot_args(position), q_rank, kv_rank, rot_dim, D, 1 if write else 0,
+            1 if norm_q else 0, self._stream))
         self.launches += 1
         return cq
 
     def latent_queries(self, q_abs, q, nh, d, rot_dim, kv_rank, D, position, ctx) -> torch.Tensor:
-        """[T, nh*D] with head h = [q_abs[t, h] (kv_rank) | rotated q[t, h, d:d+rot_dim] | 0]."""
+        """[T, nh*D] with head h = [q_abs[t, h] (kv_rank) | rotated q[t, h, d:d+rot_dim] | 0]; the heads of q are the
+        first nh * (d + rot_dim) columns of its rows."""
         T = q.shape[0]
-        assert q.is_contiguous() and q_abs.is_contiguous() and q.shape[1] == nh * (d + rot_dim) and q_abs.shape[1] == nh * kv_rank
+        assert q.is_contiguous() and q_abs.is_contiguous() and q.shape[1] >= nh * (d + rot_dim) and q_abs.shape[1] == nh * kv_rank
         out = torch.empty((T, nh * D), dtype=q.dtype, device=self.device)
-        table = position.table if position is not None else None
         _check(self.core, self.core.pl_latent_q(self._p(q_abs), self._p(q), self._code(q), T, self._p(out),
-                                                self._p(ctx.positions), self._p(ctx.token_seq), self._p(table),
-                                                table.shape[0] if table is not None else 0,
-                                                position.rotary_dim if position is not None else 0, nh, d, rot_dim, kv_rank,
-                                                D, self._stream))
+                                                self._p(ctx.positions), self._p(ctx.token_seq), *self._rot_args(position),
+                                                nh, d, rot_dim, kv_rank, D, q.shape[1], self._stream))
         self.launches += 1
         return out
 
@@ -667,23 +673,80 @@ class CudaOps:
         return out
 
     # ---- mixers with a state of fixed size: convolution + gated recurrence, gated linear attention --------------
-    def causal_conv(self, yx, col0, C, b_in, conv_w, conv_b, state, ctx):
+    def causal_conv(self, yx, col0, C, b_in, conv_w, conv_b, state, ctx, activation=None, low=True):
         """u = conv(yx[:, col0:col0+C] + b_in[col0:col0+C]) + conv_b per channel, causal, `taps` wide; the request's
         last taps-1 inputs are the first (taps-1)*C floats of its state slot and are replaced by the new ones.
-        Returns (u float32 [T, C], u in the compute dtype)."""
+        Either bias may be None; `activation` "silu" is applied to the result.
+        Returns (u float32 [T, C], u in the compute dtype, or None without `low`)."""
         lib = load_module("recurrent")
         T, ld = yx.shape
         taps = conv_w.shape[1]
         assert yx.is_contiguous() and state.dtype == torch.float32 and state.is_contiguous() and state.dim() == 2
         assert conv_w.dtype == torch.float32 and conv_w.shape == (C, taps) and conv_w.is_contiguous()
         u = torch.empty((T, C), dtype=torch.float32, device=self.device)
-        low = u if yx.dtype == torch.float32 else torch.empty((T, C), dtype=yx.dtype, device=self.device)
+        if activation not in (None, "silu"):
+            raise KernelError(f"causal_conv: activation {activation!r} (silu or none)")
+        if not low:
+            low = None
+        else:
+            low = u if yx.dtype == torch.float32 else torch.empty((T, C), dtype=yx.dtype, device=self.device)
         _check(lib, lib.pl_causal_conv(self._p(yx), self._code(yx), ld, col0, C, self._p(b_in), self._p(conv_w),
                                        self._p(conv_b), taps, self._p(state), c_longlong(state.shape[1]),
                                        self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), ctx.num_seqs, max(T, 1),
-                                       self._p(u), self._p(low) if low is not u else c_void_p(0), self._stream))
+                                       self._p(u), self._p(low) if low is not None and low is not u else c_void_p(0),
+                                       1 if activation == "silu" else 0, self._stream))
         self.launches += 1
         return u, low
+
+    def delta_rule_scan(self, u, proj, gate_col0, decay_rate, decay_bias, H, G, d, dv, unit_eps, q_scale, state_off, state,
+                        ctx) -> torch.Tensor:
+        """The gated delta rule's recurrence.  u float32 [T, q: G*d | k: G*d | v: H*dv] (convolved and activated; q and k
+        are made unit vectors in place, q also times `q_scale`); proj columns [gate_col0, +2H) hold [b: H | a: H]:
+        beta = sigmoid(b), g = exp(decay_rate * softplus(a + decay_bias)).  Per value head (q/k head h // (H // G)):
+        S <- g S; w = beta (v - S^T k); S <- S + k w^T; o = S^T q.  S lives `state_off` floats into the request's
+        state slot as [H][dv][d] float32 and is updated in place.  Returns o float32 [T, H*dv]."""
+        lib = load_module("recurrent")
+        T, C = u.shape
+        assert u.dtype == torch.float32 and u.is_contiguous() and proj.is_contiguous() and C == 2 * G * d + H * dv
+        assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] >= state_off + H * dv * d
+        assert decay_rate.dtype == torch.float32 and decay_bias.dtype == torch.float32 and decay_rate.numel() == H
+        o = torch.empty((T, H * dv), dtype=torch.float32, device=self.device)
+        bg = torch.empty((T, 2 * H), dtype=torch.float32, device=self.device)
+        _check(lib, lib.pl_delta_rule(self._p(u), C, self._p(proj), self._code(proj), proj.shape[1], gate_col0,
+                                      self._p(decay_rate), self._p(decay_bias), H, G, d, dv, c_float(unit_eps), c_float(q_scale),
+                                      self._p(bg), self._p(state), c_longlong(state.shape[1]), c_longlong(state_off),
+                                      self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), ctx.num_seqs, c_longlong(T),
+                                      self._p(o), self._stream))
+        self.launches += 2
+        return o
+
+    # ---- two branches that are normed before they meet ---------------------------------
+    def normed_pair_sum(self, a, b, wa, wb, sa, sb, eps) -> torch.Tensor:
+        """sa * rms_norm(a) * wa + sb * rms_norm(b) * wb as float32 (norms over the row, eps inside the root)."""
+        rows, W = a.shape
+        assert a.is_contiguous() and b.is_contiguous() and a.shape == b.shape and a.dtype == b.dtype
+        assert wa.dtype == torch.float32 and wb.dtype == torch.float32 and wa.numel() == W and wb.numel() == W
+        out = torch.empty((rows, W), dtype=torch.float32, device=self.device)
+        _check(self.core, self.core.pl_normed_pair(self._p(a), self._p(b), self._code(a), self._p(wa), self._p(wb), c_float(sa),
+                                                   c_float(sb), c_float(eps), c_void_p(0), self._p(out), c_void_p(0), 0,
+                                                   c_float(0.0), c_void_p(0), 0, c_longlong(rows), W, self._stream))
+        self.launches += 1
+        return out
+
+    def normed_pair_add_rms_norm(self, x, a, b, wa, wb, sa, sb, pair_eps, norm_w, eps) -> torch.Tensor:
+        """x += sa * rms_norm(a) * wa + sb * rms_norm(b) * wb (float32 stream, in place), then RMSNorm(x) * norm_w in the
+        compute dtype: one kernel."""
+        rows, W = x.shape
+        assert x.dtype == torch.float32 and x.is_contiguous() and a.shape == x.shape and b.shape == x.shape
+        assert a.is_contiguous() and b.is_contiguous() and a.dtype == b.dtype
+        assert wa.dtype == torch.float32 and wb.dtype == torch.float32 and wa.numel() == W and wb.numel() == W
+        y = torch.empty((rows, W), dtype=self.compute_dtype, device=self.device)
+        _check(self.core, self.core.pl_normed_pair(self._p(a), self._p(b), self._code(a), self._p(wa), self._p(wb), c_float(sa),
+                                                   c_float(sb), c_float(pair_eps), self._p(x), c_void_p(0), self._p(norm_w),
+                                                   self._code(norm_w), c_float(eps), self._p(y), self._code(y),
+                                                   c_longlong(rows), W, self._stream))
+        self.launches += 1
+        return y
 
     def gated_recurrence(self, gates, b_gates, u, yx, b_in, rate, blocks, taps, state, ctx) -> torch.Tensor:
         """S_t = a S_(t-1) + sqrt(1 - a^2) sigmoid(g_i) u_t with a = exp(rate * sigmoid(g_r)); returns
@@ -745,7 +808,8 @@ class CudaOps:
 
     # ---- routed experts ----------------------------------------------------------
     def routed_experts(self, h, w_router, w_gate_up, w_down, top_k: int, activation: str = "silu", shared=None,
-                       shared_activation: str = "silu") -> torch.Tensor:
+                       shared_activation: str = "silu", activation_limit: float = 0.0, scoring: str = "softmax_top",
+                       groups=None) -> torch.Tensor:
         """The feed-forward of routed experts for the step's tokens: float32 [T, D].
 
         w_router [E (+1) or more, D]: the router's rows and, with a shared expert, the row of its gate (further rows
@@ -756,7 +820,10 @@ class CudaOps:
         experts' two products over tiles of that list (bfloat16: mma.sync tiles of 64 pairs, or of 16 when
         experts get few pairs as in decoding, or, with many pairs per expert, the grouped form of the tcgen05
         product over rows gathered in sorted order; float32 and odd sizes: FFMA chains in k order); the sum.
-        Nothing is read back, so the step can be captured."""
+        Nothing is read back, so the step can be captured.  `scoring` "sigmoid": the scores sigmoid(z) choose and are the
+        weights as they are; `groups` (count, keep, best): only experts of the `keep` groups (of `count` equal groups
+        of neighbours) with the largest sum of their `best` largest scores can be chosen.  `activation`
+        "swish_clamped" takes `activation_limit`."""
         h = self.materialize(h)
         assert h.is_contiguous() and w_gate_up.is_contiguous() and w_down.is_contiguous() and w_router.is_contiguous()
         T, D = h.shape
@@ -771,8 +838,15 @@ class CudaOps:
         top_w = torch.empty(pairs, dtype=torch.float32, device=dev)
         gate = torch.empty(T, dtype=torch.float32, device=dev) if shared is not None else None
         z = self.linear(h, w_router, out_float32=True)          # float32 logits (and the shared expert's gate)
-        _check(lib, lib.pl_moe_topk(self._p(z), z.shape[1], T, E, top_k, 1 if shared is not None else 0,
-                                    self._p(top_idx), self._p(top_w), self._p(gate), self._stream))
+        if scoring == "sigmoid":
+            if shared is not None:
+                raise KernelError("routed_experts: a shared expert's gate rides with the softmax scoring only")
+            count, keep, best = groups if groups is not None else (0, 0, 0)
+            _check(lib, lib.pl_moe_sigmoid_topk(self._p(z), z.shape[1], T, E, top_k, count, keep, best, self._p(top_idx),
+                                                self._p(top_w), self._stream))
+        else:
+            _check(lib, lib.pl_moe_topk(self._p(z), z.shape[1], T, E, top_k, 1 if shared is not None else 0,
+                                        self._p(top_idx), self._p(top_w), self._p(gate), self._stream))
         tensor_cores = h.dtype == torch.bfloat16 and D % 8 == 0 and F % 8 == 0
         # Many pairs per expert (prompt portions): the experts' products run on the tcgen05 kernel of the dense
         # layers in its grouped form, over rows gathered in the order of the sorted list (tiles of 256 pairs).
@@ -787,27 +861,27 @@ class CudaOps:
         place = torch.empty(pairs, dtype=torch.int32, device=dev) if grouped_tc else None
         _check(lib, lib.pl_moe_align(self._p(top_idx), pairs, E, BM, cap, self._p(sorted_pairs),
                                      self._p(tile_expert), self._p(n_tiles), self._p(place), self._stream))
-        act = ACTIVATIONS[activation]
+        act, lim = EXPERT_ACTIVATIONS[activation], c_float(activation_limit)
         if grouped_tc:
             xs = torch.empty((cap, D), dtype=h.dtype, device=dev)
             _check(lib, lib.pl_moe_gather(self._p(h), D, top_k, self._p(sorted_pairs), self._p(n_tiles), BM, cap, pairs, D,
                                           self._p(xs), self._stream))
             inter = torch.empty((cap, F), dtype=h.dtype, device=dev)
             _check(self.core, self.core.pl_gemm_tc_grouped(self._p(xs), D, self._p(w_gate_up), self._p(inter), F, cap, F, D,
-                                                           2, act, E, self._p(n_tiles), self._p(tile_expert), self._stream))
+                                                           2, act, lim, E, self._p(n_tiles), self._p(tile_expert), self._stream))
             # (each expert's output is rounded to bfloat16, as a dense layer's branch is; the weighted sum is float32)
             pair_out = torch.empty((cap, D), dtype=torch.bfloat16, device=dev)
             _check(self.core, self.core.pl_gemm_tc_grouped(self._p(inter), F, self._p(w_down), self._p(pair_out), D, cap, D, F,
-                                                           0, act, E, self._p(n_tiles), self._p(tile_expert), self._stream))
+                                                           0, act, lim, E, self._p(n_tiles), self._p(tile_expert), self._stream))
             self.launches += 5
         else:
             inter = torch.empty((pairs, F), dtype=h.dtype, device=dev)
             _check(lib, lib.pl_moe_gemm(self._p(h), D, top_k, self._p(w_gate_up), self._p(inter), F, self._p(sorted_pairs),
-                                        self._p(tile_expert), self._p(n_tiles), c_void_p(0), pairs, F, D, 1, act, code, BM,
+                                        self._p(tile_expert), self._p(n_tiles), c_void_p(0), pairs, F, D, 1, act, lim, code, BM,
                                         max_tiles, 1 if tensor_cores else 0, self._stream))
             pair_out = torch.empty((pairs, D), dtype=torch.float32, device=dev)
             _check(lib, lib.pl_moe_gemm(self._p(inter), F, 1, self._p(w_down), self._p(pair_out), D, self._p(sorted_pairs),
-                                        self._p(tile_expert), self._p(n_tiles), self._p(top_w), pairs, D, F, 0, act, code, BM,
+                                        self._p(tile_expert), self._p(n_tiles), self._p(top_w), pairs, D, F, 0, act, lim, code, BM,
                                         max_tiles, 1 if tensor_cores else 0, self._stream))
             self.launches += 4
         s = None
@@ -917,14 +991,15 @@ class CudaOps:
                                     chunk=chunk)
 
     def paged_attention(self, qkv, nh, nkv, d, kv, block_table, ctx, scale, window, softcap=None, slopes=None,
-                        rope=None, chunk=None, dist_bias=None):
+                        rope=None, chunk=None, dist_bias=None, sink=None):
         """Attention of the step's tokens over the paged cache.  `softcap` (scores become
         softcap * tanh(score / softcap)) and `slopes` (a float32 tensor [nh]: head h adds
         slopes[h] * (key position - query position) to its scores) modify the scores; both off
         by default; `dist_bias` (float32 [nh, L]) adds dist_bias[h, min(query position - key position, L - 1)];
         `chunk` c lets a query at position p see the keys from p - p % c on only.  `rope` (a prepared rotary encoding; only where the step runs as clusters, see
         `qkv_attention`): qkv is the unrotated projection, and the kernel rotates q and the step's own
-        keys and writes those keys and values to the cache itself."""
+        keys and writes those keys and values to the cache itself.  `sink` (float32 [nh]): the softmax's denominator
+        of head h also holds exp(sink[h]), a term without key or value that counts once however the keys are split."""
         T = ctx.num_tokens
         plan = ctx.attention_plans[attention_plan_key(nh, nkv, window, d, chunk)]
         out = torch.empty((T, nh * d), dtype=qkv.dtype, device=self.device)
@@ -952,6 +1027,9 @@ class CudaOps:
             assert (dist_bias.dtype == torch.float32 and dist_bias.dim() == 2 and dist_bias.shape[0] == nh
                     and dist_bias.is_contiguous() and dist_bias.is_cuda)
             p.dist_bias, p.dist_len = dist_bias.data_ptr(), dist_bias.shape[1]
+        if sink is not None:
+            assert sink.dtype == torch.float32 and sink.numel() == nh and sink.is_contiguous() and sink.is_cuda
+            p.sink = sink.data_ptr()
         ps = kv.shape[3]
         p.ps_shift = ps.bit_length() - 1 if ps & (ps - 1) == 0 else -1
         p.counters = 0
