@@ -146,9 +146,11 @@ def parallel_mixer(h, w, p, m, eps):
     return 0.5 * (rms(a, w[p + "left.out"], eps) + rms(b, w[p + "right.out"], eps))
 
 
-def router(h, w_router, r):
+def router(h, w_router, r, margins=None):
     """(chosen experts [n, top], their weights [n, top]): sigmoid scores; the experts form `groups.count` equal
-    groups of neighbours, a group scores the sum of its two best, only the `groups.keep` best groups may be chosen."""
+    groups of neighbours, a group scores the sum of its two best, only the `groups.keep` best groups may be chosen.
+    `margins` (a list) collects how far the closest call was: the smallest gap between what was kept or chosen and
+    what came next."""
     s = torch.sigmoid(h @ w_router.T)
     n, E = s.shape
     allowed = torch.ones(n, E, dtype=torch.bool)
@@ -158,9 +160,17 @@ def router(h, w_router, r):
         gs = s.view(n, groups["count"], size)
         score = gs.topk(min(2, size), dim=-1).values.sum(-1)
         best = score.topk(groups["keep"], dim=-1).indices
+        if margins is not None and groups["keep"] < groups["count"]:
+            ranked = score.sort(dim=-1, descending=True).values
+            margins.append(float((ranked[:, groups["keep"] - 1] - ranked[:, groups["keep"]]).min()))
         keep = torch.zeros(n, groups["count"], dtype=torch.bool).scatter_(1, best, True)
         allowed = keep[:, :, None].expand(n, groups["count"], size).reshape(n, E)
-    idx = s.masked_fill(~allowed, -1.0).topk(r["top"], dim=-1).indices
+    masked = s.masked_fill(~allowed, -1.0)
+    idx = masked.topk(r["top"], dim=-1).indices
+    if margins is not None and r["top"] < E:
+        ranked = masked.sort(dim=-1, descending=True).values
+        gap = ranked[:, r["top"] - 1] - ranked[:, r["top"]]
+        margins.append(float(gap[ranked[:, r["top"]] >= 0].min()) if (ranked[:, r["top"]] >= 0).any() else 1.0)
     return idx, s.gather(1, idx)
 
 
@@ -170,8 +180,8 @@ def expert(h, w, p, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].T
 
 
-def routed_experts(h, w, p, mlp):
-    idx, wt = router(h, w[p + "router"], mlp["router"])
+def routed_experts(h, w, p, mlp, margins=None):
+    idx, wt = router(h, w[p + "router"], mlp["router"], margins)
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=F)
     for e in range(mlp["router"]["experts"]):
         tok, slot = (idx == e).nonzero(as_tuple=True)
@@ -180,7 +190,7 @@ def routed_experts(h, w, p, mlp):
     return out
 
 
-def forward(cfg, weights, tokens):
+def forward(cfg, weights, tokens, margins=None):
     w = {k: (v.to(F) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
@@ -199,7 +209,15 @@ def forward(cfg, weights, tokens):
             raise ValueError(lay["type"])
         x = x + y
         if lay.get("mlp") is not None:
-            x = x + routed_experts(rms(x, w[p + "norm2"], eps), w, p + "mlp.", lay["mlp"])
+            x = x + routed_experts(rms(x, w[p + "norm2"], eps), w, p + "mlp.", lay["mlp"], margins)
         after.append(x)
     logits = rms(x, w["final.norm"], eps) @ w["head"].T
     return logits, torch.stack(after)
+
+
+def greedy_generate(cfg, weights, prompt, n):
+    """`n` tokens after `prompt`, each the arg-max of the whole sequence's last logits."""
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(forward(cfg, weights, toks)[0][-1].argmax()))
+    return toks[len(prompt):]
