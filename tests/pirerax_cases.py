@@ -2,7 +2,8 @@
 layers, and helpers to write their folders with random weights and to ask the plain model.
 
 The weights are drawn here so that a fault shows: sinks of the size of the scores, decays between about 0.4 and 0.99
-per token, beta away from 0 and 1, convolution taps of weight, norm weights away from 1.
+per token, beta away from 0 and 1, convolution taps of weight, norm weights away from 1; the delta rule's queries lean
+on their keys (see `draw_weights`).
 """
 
 from __future__ import annotations
@@ -138,8 +139,14 @@ def draw_weights(hf_cfg: dict, seed: int) -> dict[str, torch.Tensor]:
             t = -3.0 + 3.0 * torch.rand(shape, generator=g)        # exp(A_log) between 0.05 and 1
         elif name.endswith(".dt_bias"):
             t = 0.5 * r
+        elif name.endswith(".right.q.conv"):
+            t = out[name.replace(".q.conv", ".k.conv")] + 0.15 * r
         elif name.endswith(".conv"):
             t = 0.5 * r
+        elif name.endswith(".right.q"):
+            # the delta rule's queries lean towards their own keys: the norm behind a nearly empty state keeps only the
+            # sign of q . k of the first tokens, which stays away from zero this way also in bfloat16
+            t = out[name[:-1] + "k"] + 0.4 * r * (1.2 / np.sqrt(shape[-1]))
         elif "norm" in name or name.endswith(".out"):
             t = 1.0 + 0.2 * r
         elif name == "embed":
