@@ -96,6 +96,17 @@ MUNAZEN_SIZES = {
     "m-tiny": dict(vocab=256, width=128, heads=4, kv_heads=2, dim=32, ff=256, rec_width=96, rec_blocks=3, conv=3,
                    gla_heads=2, gla_dim=16, gla_vdim=32, streams=2, norm_groups=2),
 }
+# Pirerax at the layer sizes of a 2k- and a 4k-wide model: attention with a sink, latent attention, attention beside the
+# gated delta rule, routed experts on every layer (the Llama beside it gets top * expert_ff as its inner size)
+PIRERAX_SIZES = {
+    "x-2k": dict(vocab=32000, width=2048, heads=16, kv_heads=4, dim=128, rot_dim=64, kv_rank=192, delta_heads=16, delta_kv=8,
+                 delta_dim=128, delta_vdim=128, conv=4, experts=32, top=4, groups=(8, 4), expert_ff=1024),
+    "x-4k": dict(vocab=32000, width=4096, heads=32, kv_heads=8, dim=128, rot_dim=64, kv_rank=192, delta_heads=32, delta_kv=16,
+                 delta_dim=128, delta_vdim=128, conv=4, experts=64, top=6, groups=(8, 4), expert_ff=1408),
+    # for trying the option out quickly; never a result
+    "x-tiny": dict(vocab=256, width=128, heads=4, kv_heads=2, dim=32, rot_dim=16, kv_rank=32, delta_heads=4, delta_kv=2,
+                   delta_dim=16, delta_vdim=32, conv=3, experts=8, top=2, groups=(4, 2), expert_ff=64),
+}
 PROMPT_LEN, DECODE_LEN, PREFILL_TOKENS, BLOCK_SIZE = 512, 256, 2048, 16
 RAGGED_PROMPTS, RAGGED_OUTPUTS = (128, 4096), (64, 512)      # the ragged serving workload: lengths drawn uniformly
 
@@ -655,6 +666,29 @@ def munazen_configs(name: str):
     return mun, llama, len(order)
 
 
+def pirerax_configs(name: str):
+    """(Pirerax configuration dict, Llama configuration dict of equal size, number of layers)."""
+    s = PIRERAX_SIZES[name]
+    heads = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5}
+    attention = dict(heads, q_temp={"coef": 0.5, "every": 1024})
+    latent = {"heads": s["heads"], "dim": s["dim"], "rot_dim": s["rot_dim"], "vdim": s["dim"], "kv_rank": s["kv_rank"],
+              "scale": (s["dim"] + s["rot_dim"]) ** -0.5, "rot": {"dims": s["rot_dim"], "base": 20000.0}}
+    par = {"left": dict(heads, rot={"dims": s["dim"] // 2, "base": 500000.0}),
+           "right": {"heads": s["delta_heads"], "kv_heads": s["delta_kv"], "dim": s["delta_dim"], "vdim": s["delta_vdim"],
+                     "conv": s["conv"]}}
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"], "limit": 7.0},
+           "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": s["groups"][0], "keep": s["groups"][1]}}}
+    order = [("parallel", par), ("latent_attention", latent), ("attention", attention), ("attention", attention), ("parallel", par),
+             ("latent_attention", latent)]
+    pir = {"architecture": "Pirerax", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+           "layers": [{"type": t, "mixer": m, "mlp": moe} for t, m in order]}
+    llama = {"architectures": ["LlamaForCausalLM"], "vocab_size": s["vocab"], "hidden_size": s["width"],
+             "intermediate_size": s["top"] * s["expert_ff"], "num_hidden_layers": len(order), "num_attention_heads": s["heads"],
+             "num_key_value_heads": s["kv_heads"], "head_dim": s["dim"], "rope_theta": 500000.0, "rms_norm_eps": 1e-6,
+             "tie_word_embeddings": False, "max_position_embeddings": 8192}
+    return pir, llama, len(order)
+
+
 def compare_with_llama(args, label: str, size: str, sizes: dict, model: dict, llama: dict, runs: int) -> dict:
     """Prefill and decode of another decoder at layer sizes of a real model (random weights drawn on the
     device) beside a Llama of equal width, heads and layer runs: device-timed with CUDA events, with the device
@@ -714,6 +748,11 @@ def munazen_compare(args) -> dict:
     return compare_with_llama(args, "munazen", args.munazen_size, MUNAZEN_SIZES[args.munazen_size], mun, llama, runs)
 
 
+def pirerax_compare(args) -> dict:
+    pir, llama, runs = pirerax_configs(args.pirerax_size)
+    return compare_with_llama(args, "pirerax", args.pirerax_size, PIRERAX_SIZES[args.pirerax_size], pir, llama, runs)
+
+
 def run_ours(args) -> dict:
     import torch
     from paged_llm_b200 import EngineConfig, LLMEngine
@@ -725,6 +764,8 @@ def run_ours(args) -> dict:
         return rokarax_compare(args)
     if args.only == "munazen":
         return munazen_compare(args)
+    if args.only == "pirerax":
+        return pirerax_compare(args)
     if args.only == "validate":
         return validate(args)
     if args.only == "sample":
@@ -923,12 +964,15 @@ def main() -> int:
                     help="with --only rokarax: the layer sizes (the Llama beside it gets the same)")
     ap.add_argument("--munazen-size", choices=sorted(MUNAZEN_SIZES), default="m-2k",
                     help="with --only munazen: the layer sizes (the Llama beside it gets the same)")
-    ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate", "sample", "pomisun", "rokarax", "munazen"], default=None,
+    ap.add_argument("--pirerax-size", choices=sorted(PIRERAX_SIZES), default="x-2k",
+                    help="with --only pirerax: the layer sizes (the Llama beside it gets the same)")
+    ap.add_argument("--only", choices=["decode", "prefill", "ragged", "mixed", "validate", "sample", "pomisun", "rokarax", "munazen",
+                                       "pirerax"], default=None,
                     help="run only the decode loop, only the prefill step, the ragged serving workload through "
                          "LLMEngine.generate, one mixed step (--batch decoding requests of --context tokens beside one "
                          "portion of --prefill-tokens), the float32 validation run, the sampler's kernels on --batch rows, or "
-                         "prefill and decode of the Pomisun, the Rokarax or the Munazen decoder beside a Llama of equal size "
-                         "(--pomisun-size, --rokarax-size, --munazen-size), and print "
+                         "prefill and decode of the Pomisun, the Rokarax, the Munazen or the Pirerax decoder beside a Llama of equal size "
+                         "(--pomisun-size, --rokarax-size, --munazen-size, --pirerax-size), and print "
                          "a short line")
     args = ap.parse_args()
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:

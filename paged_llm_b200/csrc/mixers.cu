@@ -638,12 +638,61 @@ __global__ void __launch_bounds__(256) normed_pair_kernel(const T* __restrict__ 
                                                           const float* __restrict__ wa, const float* __restrict__ wb, float sa,
                                                           float sb, float pair_eps, float* __restrict__ x,
                                                           float* __restrict__ sum_out, const TW* __restrict__ nw, float eps,
-                                                          TY* __restrict__ y, int W) {
+                                                          TY* __restrict__ y, int W, int vec) {
     extern __shared__ float rowv[];
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * W;
+    if (vec) {
+        // W % 4 == 0 and W <= 16 * threads: both rows live in registers, four values per access
+        constexpr int IT = 4;
+        float4 va[IT], vb[IT];
+        float ssa = 0.f, ssb = 0.f;
+#pragma unroll
+        for (int i = 0; i < IT; ++i) {
+            const int c = (threadIdx.x + i * 256) * 4;
+            va[i] = vb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < W) {
+                va[i] = Quad4<T>::load(a + base + c);
+                vb[i] = Quad4<T>::load(b + base + c);
+                ssa += va[i].x * va[i].x + va[i].y * va[i].y + va[i].z * va[i].z + va[i].w * va[i].w;
+                ssb += vb[i].x * vb[i].x + vb[i].y * vb[i].y + vb[i].z * vb[i].z + vb[i].w * vb[i].w;
+            }
+        }
+        const float ra = sa / sqrtf(block_sum(ssa, red) / (float)W + pair_eps);
+        const float rb = sb / sqrtf(block_sum(ssb, red) / (float)W + pair_eps);
+        float ssx = 0.f;
+#pragma unroll
+        for (int i = 0; i < IT; ++i) {
+            const int c = (threadIdx.x + i * 256) * 4;
+            if (c < W) {
+                const float4 ga = Quad4<float>::load(wa + c), gb = Quad4<float>::load(wb + c);
+                float4 v = make_float4(va[i].x * ra * ga.x + vb[i].x * rb * gb.x, va[i].y * ra * ga.y + vb[i].y * rb * gb.y,
+                                       va[i].z * ra * ga.z + vb[i].z * rb * gb.z, va[i].w * ra * ga.w + vb[i].w * rb * gb.w);
+                if (x != nullptr) {
+                    const float4 xv = Quad4<float>::load(x + base + c);
+                    v = make_float4(v.x + xv.x, v.y + xv.y, v.z + xv.z, v.w + xv.w);
+                    Quad4<float>::store(x + base + c, v);
+                    ssx += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                } else {
+                    Quad4<float>::store(sum_out + base + c, v);
+                }
+                va[i] = v;
+            }
+        }
+        if (x == nullptr) return;
+        const float rx = 1.0f / sqrtf(block_sum(ssx, red) / (float)W + eps);
+#pragma unroll
+        for (int i = 0; i < IT; ++i) {
+            const int c = (threadIdx.x + i * 256) * 4;
+            if (c < W) {
+                const float4 g = Quad4<TW>::load(nw + c);
+                Quad4<TY>::store(y + base + c, make_float4(va[i].x * rx * g.x, va[i].y * rx * g.y, va[i].z * rx * g.z, va[i].w * rx * g.w));
+            }
+        }
+        return;
+    }
     float ssa = 0.f, ssb = 0.f;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         const float va = to_float(a[base + c]), vb = to_float(b[base + c]);
@@ -673,8 +722,11 @@ template <typename T, typename TW, typename TY>
 static int launch_normed_pair(const void* a, const void* b, const float* wa, const float* wb, float sa, float sb, float pair_eps,
                               float* x, float* sum_out, const void* nw, float eps, void* y, long long rows, int W,
                               cudaStream_t stream) {
-    PL_CUDA(launch_pdl(normed_pair_kernel<T, TW, TY>, dim3((unsigned)rows), dim3(256), x != nullptr ? (size_t)W * 4 : 0, stream,
-                       (const T*)a, (const T*)b, wa, wb, sa, sb, pair_eps, x, sum_out, (const TW*)nw, eps, (TY*)y, W));
+    const int vec = W % 4 == 0 && W <= 16 * 256 &&
+                    (((uintptr_t)a | (uintptr_t)b | (uintptr_t)wa | (uintptr_t)wb | (uintptr_t)x | (uintptr_t)sum_out | (uintptr_t)nw |
+                      (uintptr_t)y) & 15) == 0;
+    PL_CUDA(launch_pdl(normed_pair_kernel<T, TW, TY>, dim3((unsigned)rows), dim3(256), x != nullptr && !vec ? (size_t)W * 4 : 0, stream,
+                       (const T*)a, (const T*)b, wa, wb, sa, sb, pair_eps, x, sum_out, (const TW*)nw, eps, (TY*)y, W, vec));
     return 0;
 }
 

@@ -504,26 +504,40 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(float* __restrict__ 
 // numbers S[:, j]) is independent of the other columns: DR_LANES lanes share it, lane l holding the key channels
 // 4 l + 32 m + (0..3), m < NPER / 4, in registers.  Per token, with the dots summed over the lanes by a butterfly:
 //     a = g (S_j . k),  c = g (S_j . q),  w = beta (v_j - a),  S_j <- g S_j + k w,  o_j = c + (q . k) w
-// q, k, v, beta and g of DR_TOK tokens at a time are staged in shared memory.  The order of every sum is fixed, so
-// a position's result is bit for bit the same however the prompt was cut and whatever else is in the batch.
-// State of a request, `state_off` floats into its slot: [H][dv][d].
+// q, k, v, beta and g of DR_TOK tokens at a time arrive in shared memory by cp.async, the next tokens while these
+// are worked on (two buffers).  Each dot runs as four chains whose sums are added in a fixed order, and q . k does not
+// wait for the state, so that the chain from token to token is a quarter of a dot, the butterfly and one multiply-add.
+// The order of every sum is fixed, so a position's result is bit for bit the same however the prompt was cut and
+// whatever else is in the batch.  State of a request, `state_off` floats into its slot: [H][dv][d].
 constexpr int DR_LANES = 8, DR_COLS = 16, DR_TOK = 16;
+
+__device__ __forceinline__ void dr_cp4(float* dst, const float* src, bool ok) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src),
+                 "r"(ok ? 4 : 0));
+}
+__device__ __forceinline__ void dr_cp16(float* dst, const float* src, bool ok) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src),
+                 "r"(ok ? 16 : 0));
+}
+
+// Floats of one staging buffer: q and k rows of DP, the block's values, beta and g.
+__host__ __device__ constexpr int dr_stage_floats(int DP) { return DR_TOK * (2 * DP + DR_COLS + 2); }
 
 template <int NPER>
 __global__ void __launch_bounds__(DR_LANES * DR_COLS) delta_scan_kernel(const float* __restrict__ u, int C, const float* __restrict__ bg,
                                                                        int H, int G, int d, int dv, float* __restrict__ state,
                                                                        long long state_stride, long long state_off,
                                                                        const int* __restrict__ cu_q, const int* __restrict__ slots,
-                                                                       float* __restrict__ out) {
+                                                                       float* __restrict__ out, int vec) {
     constexpr int DP = NPER * DR_LANES;                             // padded key size
-    __shared__ __align__(16) float qs[DR_TOK][DP], ks[DR_TOK][DP];
-    __shared__ float vs[DR_TOK][DR_COLS], bs[DR_TOK], gs[DR_TOK];
+    constexpr int THREADS = DR_LANES * DR_COLS;
+    extern __shared__ __align__(16) float dr_smem[];
     const int s = blockIdx.x, h = blockIdx.y;
     const int slot = slots[s];
     const int q0 = cu_q[s], nq = cu_q[s + 1] - q0;
     if (slot < 0 || nq <= 0) return;
     const int tid = threadIdx.x, lane = tid % DR_LANES, col = tid / DR_LANES;
-    const int j = blockIdx.z * DR_COLS + col;
+    const int j0 = blockIdx.z * DR_COLS, j = j0 + col;
     const bool live = j < dv;
     const int kvh = h / (H / G);
     float* sp = state + (size_t)slot * state_stride + state_off + ((size_t)h * dv + (live ? j : 0)) * d;
@@ -535,40 +549,79 @@ __global__ void __launch_bounds__(DR_LANES * DR_COLS) delta_scan_kernel(const fl
     }
     const float* uq = u + (size_t)q0 * C + (size_t)kvh * d;
     const float* uk = uq + (size_t)G * d;
-    const float* uv = u + (size_t)q0 * C + (size_t)2 * G * d + (size_t)h * dv + blockIdx.z * DR_COLS;
-    for (int t0 = 0; t0 < nq; t0 += DR_TOK) {
+    const float* uv = u + (size_t)q0 * C + (size_t)2 * G * d + (size_t)h * dv + j0;
+    const float* bgp = bg + (size_t)q0 * 2 * H + h;
+
+    auto stage = [&](int t0, int buf) {
+        float* qs = dr_smem + buf * dr_stage_floats(DP);
+        float* ks = qs + DR_TOK * DP;
+        float* vs = ks + DR_TOK * DP;
+        float* bs = vs + DR_TOK * DR_COLS;
         const int nt = min(DR_TOK, nq - t0);
-        __syncthreads();
-        for (int e = tid; e < nt * DP; e += DR_LANES * DR_COLS) {
-            const int tt = e / DP, ch = e - tt * DP;
-            qs[tt][ch] = ch < d ? uq[(size_t)(t0 + tt) * C + ch] : 0.f;
-            ks[tt][ch] = ch < d ? uk[(size_t)(t0 + tt) * C + ch] : 0.f;
+        if (vec) {
+            for (int e = tid; e < DR_TOK * (DP / 4); e += THREADS) {
+                const int tt = e / (DP / 4), ch = (e - tt * (DP / 4)) * 4;
+                const bool in = tt < nt && ch < d;
+                const size_t off = (size_t)(t0 + (in ? tt : 0)) * C + (in ? ch : 0);
+                dr_cp16(qs + tt * DP + ch, uq + off, in);
+                dr_cp16(ks + tt * DP + ch, uk + off, in);
+            }
+        } else {
+            for (int e = tid; e < DR_TOK * DP; e += THREADS) {
+                const int tt = e / DP, ch = e - tt * DP;
+                const bool in = tt < nt && ch < d;
+                const size_t off = (size_t)(t0 + (in ? tt : 0)) * C + (in ? ch : 0);
+                dr_cp4(qs + e, uq + off, in);
+                dr_cp4(ks + e, uk + off, in);
+            }
         }
-        for (int e = tid; e < nt * DR_COLS; e += DR_LANES * DR_COLS) {
+        for (int e = tid; e < DR_TOK * DR_COLS; e += THREADS) {
             const int tt = e / DR_COLS, c = e - tt * DR_COLS;
-            vs[tt][c] = blockIdx.z * DR_COLS + c < dv ? uv[(size_t)(t0 + tt) * C + c] : 0.f;
+            const bool in = tt < nt && j0 + c < dv;
+            dr_cp4(vs + e, uv + (size_t)(t0 + (in ? tt : 0)) * C + (in ? c : 0), in);
         }
-        if (tid < nt) {
-            bs[tid] = bg[(size_t)(q0 + t0 + tid) * 2 * H + h];
-            gs[tid] = bg[(size_t)(q0 + t0 + tid) * 2 * H + H + h];
+        if (tid < 2 * DR_TOK) {
+            const int tt = tid >> 1, which = tid & 1;                // beta, then g
+            const bool in = tt < nt;
+            dr_cp4(bs + which * DR_TOK + tt, bgp + (size_t)(t0 + (in ? tt : 0)) * 2 * H + which * H, in);
+        }
+        asm volatile("cp.async.commit_group;\n" ::);
+    };
+
+    stage(0, 0);
+    int buf = 0;
+    for (int t0 = 0; t0 < nq; t0 += DR_TOK, buf ^= 1) {
+        const int nt = min(DR_TOK, nq - t0);
+        if (t0 + DR_TOK < nq) {
+            stage(t0 + DR_TOK, buf ^ 1);
+            asm volatile("cp.async.wait_group 1;\n" ::);
+        } else {
+            asm volatile("cp.async.wait_group 0;\n" ::);
         }
         __syncthreads();
+        const float* qs = dr_smem + buf * dr_stage_floats(DP);
+        const float* ks = qs + DR_TOK * DP;
+        const float* vs = ks + DR_TOK * DP;
+        const float* bs = vs + DR_TOK * DR_COLS;
+        const float* gs = bs + DR_TOK;
         for (int tt = 0; tt < nt; ++tt) {
             float kr[NPER], qr[NPER];
 #pragma unroll
             for (int m = 0; m < NPER / 4; ++m) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&ks[tt][m * 32 + lane * 4]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&qs[tt][m * 32 + lane * 4]);
+                const float4 k4 = *reinterpret_cast<const float4*>(ks + tt * DP + m * 32 + lane * 4);
+                const float4 q4 = *reinterpret_cast<const float4*>(qs + tt * DP + m * 32 + lane * 4);
                 kr[4 * m] = k4.x, kr[4 * m + 1] = k4.y, kr[4 * m + 2] = k4.z, kr[4 * m + 3] = k4.w;
                 qr[4 * m] = q4.x, qr[4 * m + 1] = q4.y, qr[4 * m + 2] = q4.z, qr[4 * m + 3] = q4.w;
             }
-            float a = 0.f, c = 0.f, qk = 0.f;                      // (q . k does not wait for the state)
+            float a4[4] = {0.f, 0.f, 0.f, 0.f}, c4[4] = {0.f, 0.f, 0.f, 0.f}, e4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < NPER; ++r) {
-                a = fmaf(S[r], kr[r], a);
-                c = fmaf(S[r], qr[r], c);
-                qk = fmaf(qr[r], kr[r], qk);
+                a4[r & 3] = fmaf(S[r], kr[r], a4[r & 3]);
+                c4[r & 3] = fmaf(S[r], qr[r], c4[r & 3]);
+                e4[r & 3] = fmaf(qr[r], kr[r], e4[r & 3]);
             }
+            float a = (a4[0] + a4[1]) + (a4[2] + a4[3]), c = (c4[0] + c4[1]) + (c4[2] + c4[3]);
+            float qk = (e4[0] + e4[1]) + (e4[2] + e4[3]);
 #pragma unroll
             for (int o = DR_LANES / 2; o > 0; o >>= 1) {
                 a += __shfl_xor_sync(0xffffffffu, a, o);
@@ -576,11 +629,12 @@ __global__ void __launch_bounds__(DR_LANES * DR_COLS) delta_scan_kernel(const fl
                 qk += __shfl_xor_sync(0xffffffffu, qk, o);
             }
             const float g = gs[tt];
-            const float w = bs[tt] * (vs[tt][col] - g * a);
+            const float w = bs[tt] * (vs[tt * DR_COLS + col] - g * a);
 #pragma unroll
             for (int r = 0; r < NPER; ++r) S[r] = fmaf(kr[r], w, g * S[r]);
             if (live && lane == 0) out[(size_t)(q0 + t0 + tt) * H * dv + (size_t)h * dv + j] = fmaf(qk, w, g * c);
         }
+        __syncthreads();                                            // the buffer is free for the copies of the chunk after next
     }
     if (live) {
 #pragma unroll
@@ -614,7 +668,19 @@ PL_EXPORT int pl_delta_rule(float* u, int C, const void* proj, int dtype, int ld
     PL_LAUNCHED("delta_prepare");
     const dim3 grid(num_seqs, H, (dv + DR_COLS - 1) / DR_COLS);
     PL_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "delta_rule: %d heads of %d values", H, dv);
-#define DELTA_SCAN(N) delta_scan_kernel<N><<<grid, DR_LANES * DR_COLS, 0, stream>>>(u, C, bg, H, G, d, dv, state, state_stride, state_off, cu_q, slots, out)
+    // 16-byte copies where every row of q and k starts on a 16-byte boundary
+    const int vec = d % 4 == 0 && C % 4 == 0 && ((uintptr_t)u & 15) == 0;
+#define DELTA_SCAN(N)                                                                                                          \
+    do {                                                                                                                       \
+        const size_t smem = (size_t)2 * dr_stage_floats(N * DR_LANES) * sizeof(float);                                         \
+        static bool opted = false;                                                                                             \
+        if (!opted && smem > 48 * 1024) {                                                                                      \
+            PL_CUDA(cudaFuncSetAttribute(delta_scan_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));       \
+            opted = true;                                                                                                      \
+        }                                                                                                                      \
+        delta_scan_kernel<N><<<grid, DR_LANES * DR_COLS, smem, stream>>>(u, C, bg, H, G, d, dv, state, state_stride, state_off, \
+                                                                         cu_q, slots, out, vec);                               \
+    } while (0)
     if (d <= 4 * DR_LANES) DELTA_SCAN(4);
     else if (d <= 8 * DR_LANES) DELTA_SCAN(8);
     else if (d <= 16 * DR_LANES) DELTA_SCAN(16);
