@@ -135,6 +135,8 @@ class CudaOps:
         self.rope_in_attention = os.environ.get("PAGED_LLM_B200_NO_ROPE_IN_ATTENTION") is None
         # long work-list ranges of decode attention in a ring of three 64-key tiles (head sizes up to 64)
         self.deep_list = os.environ.get("PAGED_LLM_B200_NO_DEEP_LIST") is None
+        # lanes that share a column of the delta rule's state (8 unless 16 or 32 is asked for, for measurements)
+        self.delta_lanes = int(os.environ.get("PAGED_LLM_B200_DELTA_LANES", "0"))
         self._argmax_ws = None            # (packed winners, arrival counters) of the multi-block argmax
         self._sample_dev = None           # the sampling parameters of a step on the device, and their pinned ring
         self._sample_ring: list = []
@@ -711,12 +713,12 @@ class CudaOps:
         assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] >= state_off + H * dv * d
         assert decay_rate.dtype == torch.float32 and decay_bias.dtype == torch.float32 and decay_rate.numel() == H
         o = torch.empty((T, H * dv), dtype=torch.float32, device=self.device)
-        bg = torch.empty((T, 2 * H), dtype=torch.float32, device=self.device)
+        bg = torch.empty((T, 2 * H + G), dtype=torch.float32, device=self.device)
         _check(lib, lib.pl_delta_rule(self._p(u), C, self._p(proj), self._code(proj), proj.shape[1], gate_col0,
                                       self._p(decay_rate), self._p(decay_bias), H, G, d, dv, c_float(unit_eps), c_float(q_scale),
                                       self._p(bg), self._p(state), c_longlong(state.shape[1]), c_longlong(state_off),
                                       self._p(ctx.cu_seqlens_q), self._p(ctx.state_slots), ctx.num_seqs, c_longlong(T),
-                                      self._p(o), self._stream))
+                                      self._p(o), self.delta_lanes, self._stream))
         self.launches += 2
         return o
 

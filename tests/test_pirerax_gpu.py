@@ -131,8 +131,14 @@ def test_latent_attention_alone(ops, dtype, W, m):
     (64, {"heads": 1, "kv_heads": 1, "dim": 200, "vdim": 17, "conv": 2}), (32, {"heads": 6, "kv_heads": 3, "dim": 64, "vdim": 64, "conv": 4}),
 ])
 def test_delta_rule_alone(ops, dtype, W, m):
-    """Every lane count of the recurrence's kernel (key sizes up to 32, 64, 128, 256), sizes that fill neither lanes nor columns."""
-    parts.check_delta(ops, "cuda", dtype, W, m, LENS, seed=7, ways=("whole", (0.6, 0.4), "decode", ("every", 2)))
+    """Every form of the recurrence's kernel (key sizes up to 32, 64, 128, 256; 8, 16 and 32 lanes per column), sizes
+    that fill neither lanes nor columns."""
+    try:
+        for lanes in (0, 16, 32):
+            ops.delta_lanes = lanes
+            parts.check_delta(ops, "cuda", dtype, W, m, LENS, seed=7, ways=("whole", (0.6, 0.4), "decode", ("every", 2)))
+    finally:
+        ops.delta_lanes = 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
