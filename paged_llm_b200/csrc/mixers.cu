@@ -183,6 +183,20 @@ struct RotTable {
     int len, rd, inter;
 };
 
+// Four consecutive elements c .. c+3 of a head after the rotation in halves (element i < rd/2 pairs with i + rd/2), for
+// rd a multiple of 8 so that a quad lies wholly in one half or behind the rotated part.  `self` and `other` are the quads
+// at c and at its partner's place, `cs` the table row.
+__device__ __forceinline__ float4 turned_quad(const float2* cs, int rd, int c, float4 self, float4 other) {
+    if (cs == nullptr || c >= rd) return self;
+    const int half = rd >> 1;
+    const bool second = c >= half;
+    const float4 t01 = *reinterpret_cast<const float4*>(cs + (second ? c - half : c));
+    const float4 t23 = *reinterpret_cast<const float4*>(cs + (second ? c - half : c) + 2);
+    const float sg = second ? 1.f : -1.f;
+    return make_float4(fmaf(self.x, t01.x, sg * other.x * t01.y), fmaf(self.y, t01.z, sg * other.y * t01.w),
+                       fmaf(self.z, t23.x, sg * other.z * t23.y), fmaf(self.w, t23.z, sg * other.w * t23.w));
+}
+
 // ------------------------------------------------------------------ norm over whole projections + cache write
 // proj row: [q: nh*d | k: nkv*d | v: nkv*dv | ...] (k and v only with has_kv).  One block per token.
 //   q' = q / sqrt(mean(q^2) + eps) * qw over all nh*d elements at once, the same for k with kw.
@@ -213,7 +227,24 @@ __global__ void normed_qkv_kernel(const T* __restrict__ proj, int ld, const floa
     float rq = 1.0f / sqrtf(block_sum(sq, red) / (float)nq + eps);
     if (t_every > 0) rq *= 1.0f + t_coef * logf((float)((max(pos, 0) + 1) / t_every) + 1.0f);
     const float2* cs = rot.table != nullptr && pos >= 0 && pos < rot.len ? rot.table + (size_t)pos * (rot.rd >> 1) : nullptr;
-    if (cs != nullptr) {
+    // the rotation four elements at a time: halves, and a rotated width that quads do not straddle
+    const bool rot_vec = vec && cs != nullptr && !rot.inter && rot.rd % 8 == 0;
+    auto weighted = [&](const T* src, const float* w, int at) {
+        const float4 a = Quad4<T>::load(src + at), g = Quad4<float>::load(w + at);
+        return make_float4(a.x * g.x, a.y * g.y, a.z * g.z, a.w * g.w);
+    };
+    auto partner = [&](int c) { return c >= rot.rd ? c : c >= (rot.rd >> 1) ? c - (rot.rd >> 1) : c + (rot.rd >> 1); };
+    if (rot_vec) {
+        for (int i = threadIdx.x * 4; i < nh * D; i += blockDim.x * 4) {
+            const int h = i / D, c = i - h * D;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < d) {
+                v = turned_quad(cs, rot.rd, c, weighted(row, qw, h * d + c), weighted(row, qw, h * d + partner(c)));
+                v = make_float4(v.x * rq, v.y * rq, v.z * rq, v.w * rq);
+            }
+            Quad4<T>::store(qo + i, v);
+        }
+    } else if (cs != nullptr) {
         for (int i = threadIdx.x; i < nh * D; i += blockDim.x) {
             const int h = i / D, c = i - h * D;
             const float v = c < d ? turned(cs, rot.rd, rot.inter, 1.f, c, [&](int e) {
@@ -247,6 +278,20 @@ __global__ void normed_qkv_kernel(const T* __restrict__ proj, int ld, const floa
     const float rk = 1.0f / sqrtf(block_sum(sk, red) / (float)nk + eps);
     if (slot < 0) return;
     const size_t head_stride = (size_t)sa.ps * D, v_off = (size_t)nkv * sa.ps * D;
+    if (rot_vec) {
+        for (int i = threadIdx.x * 4; i < nkv * D; i += blockDim.x * 4) {
+            const int h = i / D, c = i - h * D;
+            float4 kk = make_float4(0.f, 0.f, 0.f, 0.f), vv = kk;
+            if (c < d) {
+                kk = turned_quad(cs, rot.rd, c, weighted(row + nq, kw, h * d + c), weighted(row + nq, kw, h * d + partner(c)));
+                kk = make_float4(kk.x * rk, kk.y * rk, kk.z * rk, kk.w * rk);
+            }
+            if (c < dv) vv = Quad4<T>::load(row + nq + nk + h * dv + c);
+            Quad4<T>::store(kv + slot + h * head_stride + c, kk);
+            Quad4<T>::store(kv + slot + v_off + h * head_stride + c, vv);
+        }
+        return;
+    }
     if (cs != nullptr) {
         for (int i = threadIdx.x; i < nkv * D; i += blockDim.x) {
             const int h = i / D, c = i - h * D;
@@ -295,8 +340,8 @@ PL_EXPORT int pl_normed_qkv_write(const void* proj, int dtype, int T, int ld, co
     RotTable rot{(const float2*)rot_table, rot_len, rot_rd, rot_inter};
     SlotArgs sa{positions, token_seq, block_table, bt_stride, num_pages, ps};
     // four elements per step where every head, row and pointer allows it
-    const int vec = d % 4 == 0 && dv % 4 == 0 && D % 4 == 0 && ld % 4 == 0 &&
-                    (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)kv | (uintptr_t)qw | (uintptr_t)kw) & 15) == 0;
+    const int vec = d % 4 == 0 && dv % 4 == 0 && D % 4 == 0 && ld % 4 == 0 && nh * d % 4 == 0 && nkv * d % 4 == 0 &&
+                    (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)kv | (uintptr_t)qw | (uintptr_t)kw | (uintptr_t)rot_table) & 15) == 0;
     if (dtype == PL_F32)
         normed_qkv_kernel<float><<<T, 256, 0, stream>>>((const float*)proj, ld, qw, kw, eps, (float*)q_out, (float*)kv, sa,
                                                         nh, nkv, d, dv, D, has_kv, write, vec, rot, t_coef, t_every);
