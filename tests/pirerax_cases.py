@@ -124,6 +124,37 @@ def generated_case(seed: int) -> dict:
             "norm": {"eps": rng.choice([1e-6, 1e-5])}, "layers": layers}
 
 
+def wide_case(seed: int) -> dict:
+    """A drawn configuration at widths of 256 to 512 with heads of 32 to 128, three to five layers: the sizes at which the
+    tensor-core kernels, four-element accesses and the larger builds of the attention kernels run."""
+    rng = random.Random(seed)
+    layers = []
+    for _ in range(rng.randint(3, 5)):
+        kind = rng.choice(["attention", "latent_attention", "parallel"])
+        if kind == "attention":
+            kv, dim = rng.choice([1, 2, 4]), rng.choice([32, 64, 128])
+            m = attention(kv * rng.choice([1, 2, 4]), kv, dim, rng.choice([dim, 48, 96]), scale=rng.choice([0.8, 1.0]) * dim ** -0.5,
+                          q_temp=rng.choice([None, (0.5, 64), (0.3, 32)]))
+        elif kind == "latent_attention":
+            m = latent(rng.choice([2, 4, 8]), rng.choice([32, 64, 96]), rng.choice([16, 32, 64]), rng.choice([32, 64, 96]),
+                       rng.choice([64, 96, 128, 160]), base=rng.choice([1e4, 2e4, 5e5]))
+        else:
+            kv, dim, g = rng.choice([1, 2, 4]), rng.choice([32, 64, 128]), rng.choice([1, 2, 4])
+            m = parallel(attention(kv * rng.choice([1, 2, 4]), kv, dim, rng.choice([dim, 64, 96])), rng.choice([dim, dim // 2, 16]),
+                         rng.choice([1e4, 1e6]), g * rng.choice([1, 2, 4]), g, rng.choice([16, 48, 64, 128]), rng.choice([32, 80, 128]),
+                         rng.choice([2, 3, 4]))
+        mlp = None
+        if rng.random() < 0.9:
+            count, per = rng.choice([1, 2, 4]), rng.choice([2, 4])
+            keep = rng.randint(1, count)
+            groups = rng.choice([None, (count, keep), (count, keep)])
+            allowed = count * per if groups is None else keep * per
+            mlp = moe(rng.choice([32, 64, 128]), rng.choice([1.0, 1.5, 7.0]), count * per, rng.randint(1, min(allowed, 4)), groups)
+        layers.append(layer(kind, m, mlp))
+    return {"architecture": "Pirerax", "vocab": rng.choice([320, 1000]), "width": rng.choice([256, 384, 512]),
+            "norm": {"eps": rng.choice([1e-6, 1e-5])}, "layers": layers}
+
+
 def draw_weights(hf_cfg: dict, seed: int) -> dict[str, torch.Tensor]:
     """Every tensor the model expects, in float32 with values that bfloat16 holds exactly."""
     arch, cfg = parse_model_config(hf_cfg)

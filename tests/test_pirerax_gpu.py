@@ -17,7 +17,7 @@ from tests import plain_pirerax as plain
 from tests import schedules
 from tests.helpers import requests_for
 from tests.pirerax_cases import (CASE_A, CASE_B, CASE_C, CASES, attention, case_folder, clear_requests, generated_case, latent,
-                                 make_folder, moe, plain_greedy, plain_logits, rounding_error)
+                                 make_folder, moe, plain_greedy, plain_logits, rounding_error, wide_case)
 
 pytestmark = pytest.mark.gpu
 
@@ -309,6 +309,22 @@ def test_generated_configurations(tmp_path, seed):
         got = schedules.collect(steps, outputs)
         for rid, toks in reqs.items():
             close(got[rid], plain_logits(folder, toks), dtype, f"generated {seed}/{dtype}/{rid}", rounding_of(folder, toks, dtype))
+
+
+@pytest.mark.parametrize("seed", [6, 10, 13])
+def test_wide_generated_configurations(tmp_path, seed):
+    """Drawn configurations at widths of 256 to 512 under a mixed schedule, float32 against the plain model and bfloat16
+    against the float32 engine (which is measured against the plain model in the same test)."""
+    hf = wide_case(seed)
+    folder = make_folder(tmp_path, hf, seed)
+    reqs = clear_requests(folder, hf["vocab"], (3, 90, 1, 33, 140), seed=seed)
+    steps, max_tokens = schedules.mixed(reqs, live=4, seed=seed)
+    a, _ = replay(folder, "float32", steps, max_tokens)
+    b, _ = replay(folder, "bfloat16", steps, max_tokens)
+    a, b = schedules.collect(steps, a), schedules.collect(steps, b)
+    for rid, toks in reqs.items():
+        close(a[rid], plain_logits(folder, toks), "float32", f"wide {seed}/float32/{rid}", rounding_of(folder, toks, "float32"))
+        close(b[rid], a[rid], "bfloat16", f"wide {seed}/bfloat16/{rid}", rounding_of(folder, toks, "bfloat16"))
 
 
 def test_greedy_generation_through_the_engine(folders):
